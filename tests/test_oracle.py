@@ -81,7 +81,8 @@ def test_t1_vs_live_collective_beyond_two_ranks(path):
     bound = sum(p.float().abs() for p in c["parts"]) * 2.0 ** -8 * c["world"]
     assert bool((d <= bound).all())
     res, norm, scale = eo.epilogue_t1(c["parts"], c["residual"], c["weight"], c["eps"], c["quant"])
-    torch.testing.assert_close(res.float(), c["residual_out"].float(), atol=2e-2, rtol=2e-2)
+    # pairwise bf16 adds of values of size ~4..8 carry ~0.03 of rounding each: looser than 2e-2
+    torch.testing.assert_close(res.float(), c["residual_out"].float(), atol=1e-1, rtol=2e-2)
     d8 = eo.fp8_ulp_distance(norm, c["norm_out"])
     assert (d8 <= 1).float().mean().item() >= 0.99      # the collective's own noise, not the oracle's
     torch.testing.assert_close(scale, c["scale"], atol=0, rtol=2e-2)
