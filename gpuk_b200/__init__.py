@@ -1,0 +1,264 @@
+"""gpuk_b200 -- B200-native tensor-parallel epilogue behind the gpuk operator API.
+
+Mirrors the reference's Python surface (``gpuk/__init__.py``): the operator aliases
+(``:18-31``), the FP8 policy constants (``:38-51``) and ``GPUKDistEnv`` (``:54-205``).  The
+operators come from ``libgpuk_b200.so`` (``torch.ops.gpuk.*``, schema strings identical to
+``src/register.cpp:5-40``), which sits on the C ABI of ``include/gpuk_b200.h``.
+
+There is no CPU or PyTorch fallback for the fused path: a missing native library is an
+ImportError, and the fused calls raise when they cannot reach the CUDA kernels.
+"""
+from __future__ import annotations
+
+import os
+from contextlib import contextmanager
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+this_dir = os.path.dirname(os.path.abspath(__file__))
+package_name = "gpuk"   # operator namespace, as in the reference (gpuk/__init__.py:11,15)
+filename = os.path.join(this_dir, "libgpuk_b200.so")
+if not os.path.exists(filename):
+    raise ImportError(
+        f"{filename} is missing: build it with `python -m gpuk_b200._build` (needs nvcc and g++; "
+        "there is no CPU fallback)")
+
+from . import cabi  # noqa: E402  (loads libgpuk_core.so first; libgpuk_b200.so links against it)
+
+torch.ops.load_library(filename)
+_ops = torch.ops.gpuk
+
+init_ar_fusion = _ops.init_ar_fusion
+destroy_ar_fusion = _ops.destroy_ar_fusion
+get_ar_fusion_barrier_handle = _ops.get_ar_fusion_barrier_handle
+get_ar_fusion_data_handle = _ops.get_ar_fusion_data_handle
+open_ar_fusion_barrier_handles = _ops.open_ar_fusion_barrier_handles
+open_ar_fusion_data_handles = _ops.open_ar_fusion_data_handles
+ar_fusion_capture_clear = _ops.ar_fusion_capture_clear
+get_ar_fusion_tensor_handle = _ops.get_ar_fusion_tensor_handle
+get_ar_fusion_tensor_offset = _ops.get_ar_fusion_tensor_offset
+get_ar_fusion_captured_handles = _ops.get_ar_fusion_captured_handles
+get_ar_fusion_captured_offsets = _ops.get_ar_fusion_captured_offsets
+open_ar_fusion_captured_handles = _ops.open_ar_fusion_captured_handles
+allreduce_inplace = _ops.allreduce_inplace
+allreduce_rms = _ops.allreduce_rms
+
+# ---------------------------------------------------------------------------------------
+# FP8 policy (gpuk/__init__.py:38-51).  The reference selects the flavour by editing these
+# module constants and ships with the AMD fnuz flavour; on B200 the default is OCP e4m3fn
+# with its full range.  `set_fp8_policy` (or GPUK_FP8_POLICY) switches to the reference's
+# own two settings.
+# ---------------------------------------------------------------------------------------
+QUANT_NONE = 0
+_POLICIES = {
+    "e4m3fn_240": (torch.float8_e4m3fn, 240, 1),      # reference policy 1 (float8.h:216-218)
+    "e4m3fnuz_120": (torch.float8_e4m3fnuz, 120, 2),  # reference policy 2 (float8.h:249-251), its default
+    "e4m3fn_448": (torch.float8_e4m3fn, 448, 3),      # OCP range, per-token dynamic scale
+}
+QUANT_STATIC_E4M3FN_448 = 4                            # one caller-supplied scale per tensor
+
+fp8 = torch.float8_e4m3fn
+fp8_max_val = 448
+fp8_policy_id = 3
+
+
+def set_fp8_policy(name: str) -> None:
+    """Select the FP8 flavour, saturation value and operator policy id for this process."""
+    global fp8, fp8_max_val, fp8_policy_id
+    if name not in _POLICIES:
+        raise ValueError(f"unknown FP8 policy {name!r}; choose from {sorted(_POLICIES)}")
+    fp8, fp8_max_val, fp8_policy_id = _POLICIES[name]
+
+
+if os.environ.get("GPUK_FP8_POLICY"):
+    set_fp8_policy(os.environ["GPUK_FP8_POLICY"])
+
+
+class _TorchOps:
+    """The operator set GPUKDistEnv drives; tests substitute a recording fake."""
+    init_ar_fusion = staticmethod(init_ar_fusion)
+    destroy_ar_fusion = staticmethod(destroy_ar_fusion)
+    get_ar_fusion_barrier_handle = staticmethod(get_ar_fusion_barrier_handle)
+    get_ar_fusion_data_handle = staticmethod(get_ar_fusion_data_handle)
+    open_ar_fusion_barrier_handles = staticmethod(open_ar_fusion_barrier_handles)
+    open_ar_fusion_data_handles = staticmethod(open_ar_fusion_data_handles)
+    ar_fusion_capture_clear = staticmethod(ar_fusion_capture_clear)
+    get_ar_fusion_captured_handles = staticmethod(get_ar_fusion_captured_handles)
+    get_ar_fusion_captured_offsets = staticmethod(get_ar_fusion_captured_offsets)
+    open_ar_fusion_captured_handles = staticmethod(open_ar_fusion_captured_handles)
+    allreduce_inplace = staticmethod(allreduce_inplace)
+    allreduce_rms = staticmethod(allreduce_rms)
+    set_device = staticmethod(lambda d: torch.cuda.set_device(d))
+    synchronize = staticmethod(lambda d: torch.cuda.synchronize(d))
+    is_capturing = staticmethod(lambda: torch.cuda.is_current_stream_capturing())
+
+
+class GPUKDistEnv:
+    """Per-process handle on the fused tensor-parallel epilogue (``gpuk/__init__.py:54-205``).
+
+    Same constructor, methods and return values as the reference class.  Differences a
+    caller can observe:
+
+    * a group of one works: the fused call runs the no-communication kernel (the reference
+      leaves ``fptr = None``, ``:72-73``, and its fused call then fails);
+    * any hidden size that is a multiple of 16 bytes is accepted (reference: 1024/2048/4096);
+    * ``allreduce_add_rms_fused`` takes two keyword-only additions, ``static_scale`` (one
+      per-tensor scale instead of per-token dynamic scales) and ``quant_type`` (override of
+      the module-level FP8 policy);
+    * inputs are never registered or copied into staging by the host, so ``capture`` /
+      ``consume_capture`` exchange nothing (they still synchronise the group as before).
+    """
+
+    _SUPPORTED_WORLD_SIZES = [2, 4, 8]
+
+    def __init__(self, group=None, device_id: int = None, max_size_in_bytes=16384 * 16384,
+                 comm_ptrs_buf_len=1024 * 256, dtype: torch.dtype = torch.bfloat16, *, _ops=None) -> None:
+        self._o = _ops or _TorchOps
+        self.group = group
+        self.device_id = device_id
+        self.rank = dist.get_rank(group=self.group)
+        self.world_size = dist.get_world_size(group=self.group)
+        self.fptr = None
+        self._IS_CAPTURING = False
+        self._IS_CAPTURED = False
+        self.disabled = False
+        self._o.set_device(self.device_id)
+
+        if self.world_size == 1:
+            return
+        if self.world_size not in GPUKDistEnv._SUPPORTED_WORLD_SIZES:
+            return
+
+        self.fptr = self._o.init_ar_fusion(self.device_id, self.rank, self.world_size, max_size_in_bytes,
+                                           comm_ptrs_buf_len)
+        barrier_handle = self._o.get_ar_fusion_barrier_handle(self.fptr)
+        data_handle = self._o.get_ar_fusion_data_handle(self.fptr)
+        self.barrier()
+        barrier_handle_list = [None] * self.world_size
+        data_handle_list = [None] * self.world_size
+        dist.all_gather_object(barrier_handle_list, barrier_handle, group=self.group)
+        dist.all_gather_object(data_handle_list, data_handle, group=self.group)
+        self._o.open_ar_fusion_barrier_handles(self.fptr, barrier_handle_list)
+        self._o.open_ar_fusion_data_handles(self.fptr, data_handle_list)
+        self.barrier()
+
+    def barrier(self):
+        self._o.set_device(self.device_id)
+        self._o.synchronize(self.device_id)
+        dist.barrier(group=self.group)
+
+    def consume_capture(self):
+        if not self.fptr:
+            return
+        self.barrier()
+        handles = self._o.get_ar_fusion_captured_handles(self.fptr)
+        offsets = self._o.get_ar_fusion_captured_offsets(self.fptr)
+        for idx in range(len(handles)):
+            handle_list = [None] * self.world_size
+            offset_list = [None] * self.world_size
+            dist.all_gather_object(handle_list, handles[idx], group=self.group)
+            dist.all_gather_object(offset_list, int(offsets[idx].item()), group=self.group)
+            self.barrier()
+            self._o.open_ar_fusion_captured_handles(self.fptr, handle_list, offset_list, idx)
+        self._o.ar_fusion_capture_clear(self.fptr)
+        self.barrier()
+
+    @contextmanager
+    def capture(self):
+        try:
+            self._IS_CAPTURING = True
+            yield
+        finally:
+            self._IS_CAPTURING = False
+            if not self.disabled:
+                self.consume_capture()
+
+    def capture_(self, input: torch.Tensor):
+        if self._o.is_capturing():
+            self._IS_CAPTURED = True
+        else:
+            if self._IS_CAPTURED:
+                self.consume_capture()
+                self._IS_CAPTURED = False
+
+    def __del__(self):
+        fptr = getattr(self, "fptr", None)
+        if fptr:
+            try:
+                self._o.destroy_ar_fusion(fptr)
+            except Exception:
+                pass
+            self.fptr = None
+
+    def _require_workspace(self):
+        if self.world_size != 1 and not self.fptr:
+            raise RuntimeError(
+                f"gpuk: world size {self.world_size} is not supported by the fused path "
+                f"(supported: 1 and {GPUKDistEnv._SUPPORTED_WORLD_SIZES})")
+
+    def allreduce_native(self, allreduce_in):
+        allreduce_out = allreduce_in.clone()
+        dist.all_reduce(allreduce_out, group=self.group)
+        return allreduce_out
+
+    def allreduce(self, allreduce_in):
+        self._require_workspace()
+        allreduce_out = allreduce_in.clone()
+        if self.world_size > 1:
+            self._o.allreduce_inplace(self.fptr, allreduce_out)
+        return allreduce_out
+
+    def allreduce_add_rms_native(self, allreduce_in, residual_in, rms_weight, eps, fp8_out=False):
+        """The PyTorch operator sequence the fused call must match (``gpuk/__init__.py:147-173``)."""
+        def rms_norm_forward(x: torch.Tensor, weight: torch.Tensor, eps: float):
+            input_dtype = x.dtype
+            variance = x.float().pow(2).mean(-1, keepdim=True)
+            x = x * torch.rsqrt(variance + eps)
+            x = x.to(input_dtype)
+            return weight * x
+        if self.world_size > 1:
+            dist.all_reduce(allreduce_in, group=self.group)
+        residual_out = allreduce_in + residual_in
+        norm_out = rms_norm_forward(residual_out, rms_weight, eps)
+        if fp8_out:
+            norm_out_scale, _ = norm_out.float().abs().max(dim=-1, keepdim=True)
+            norm_out_scale = norm_out_scale / fp8_max_val
+            norm_out = norm_out / norm_out_scale
+            norm_out.clamp_(min=-fp8_max_val, max=fp8_max_val)
+            norm_out = norm_out.to(fp8)
+            return residual_out, norm_out, norm_out_scale
+        scale_out = torch.empty(allreduce_in.shape[0], 1, dtype=torch.float32, device=allreduce_in.device)
+        return residual_out, norm_out, scale_out
+
+    def allreduce_add_rms_fused(self, allreduce_in, residual_in, rms_weight, eps, fp8_out=False, *,
+                                static_scale: Optional[torch.Tensor] = None, quant_type: Optional[int] = None):
+        """Fused all-reduce + residual add + RMSNorm (+ FP8), ``gpuk/__init__.py:175-205``.
+
+        Returns ``(residual_out, norm_out, scale_out)`` like the reference.  With
+        ``static_scale`` (a one-element fp32 CUDA tensor, or a float) the output is quantised
+        with that single scale and ``scale_out`` is that tensor.
+        """
+        self._require_workspace()
+        self.capture_(allreduce_in)
+        residual_out = torch.empty_like(residual_in)
+        if static_scale is not None:
+            fp8_out = True
+            qt = QUANT_STATIC_E4M3FN_448
+            if not isinstance(static_scale, torch.Tensor):
+                static_scale = torch.tensor([float(static_scale)], dtype=torch.float32, device=allreduce_in.device)
+            scale_out = static_scale.reshape(-1)
+            out_dtype = torch.float8_e4m3fn
+        elif fp8_out:
+            qt = fp8_policy_id if quant_type is None else quant_type
+            out_dtype = torch.float8_e4m3fnuz if qt == 2 else torch.float8_e4m3fn
+            scale_out = torch.empty(allreduce_in.shape[0], 1, dtype=torch.float32, device=allreduce_in.device)
+        else:
+            qt = QUANT_NONE
+            out_dtype = allreduce_in.dtype
+            scale_out = torch.empty(1, dtype=torch.float32, device=allreduce_in.device)
+        norm_out = torch.empty_like(allreduce_in, dtype=out_dtype)
+        self._o.allreduce_rms(self.fptr or 0, allreduce_in, residual_in, rms_weight, residual_out, norm_out,
+                              scale_out, eps, qt)
+        return residual_out, norm_out, scale_out

@@ -1,0 +1,255 @@
+// Device-side building blocks shared by every kernel of the tensor-parallel epilogue:
+// 16-byte vector access, element traits with explicit rounding, warp/block reductions,
+// the hardware FP8 cast, and the cross-GPU flag primitives with bounded waits.
+//
+// Replaces, for sm_100a only, the reference's src/common/kernel_utils.h:29-99 (vec_t,
+// warp_reduce, block_reduce), src/common/communicator.h:12-36,79-113 (st_flag, ld_flag,
+// SyncComm) and the software FP8 cast of src/common/float8.h:17-150.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gpuk {
+
+constexpr int kMaxRanks = 8;        // communicator.h:57
+constexpr int kMaxBlocks = 2048;    // CTA indices that own a flag row (reference: 80, communicator.h:58)
+constexpr int kFlagStages = 2;      // stage 0: "my push has landed", stage 1: "my reduced slice has landed"
+constexpr int kStatusWords = 8;
+
+// ---------------------------------------------------------------------------------------
+// quantisation policy (host picks it from the operator's quant_type argument)
+// ---------------------------------------------------------------------------------------
+enum QuantMode : int { kQuantNone = 0, kQuantDynamic = 1, kQuantStatic = 2 };
+
+struct Quant {
+    int mode;        // QuantMode
+    int fnuz;        // 1: e4m3fnuz bit patterns (bias 8, no negative zero), 0: e4m3fn
+    float fp8_max;   // saturation value used for the scale and the clamp (240 / 120 / 448)
+};
+
+// ---------------------------------------------------------------------------------------
+// device-resident state of one rank's workspace (local, never mapped by peers)
+// ---------------------------------------------------------------------------------------
+struct LocalState {
+    uint32_t epoch;       // base value for this call's flags; advanced by the last CTA of every call
+    uint32_t os_seq;      // number of one-shot calls so far; its low bit selects the one-shot buffer
+    uint32_t ticket;      // CTAs that have finished the current call
+    uint32_t abort;       // set once a wait has run out, so that later waits give up at once
+    unsigned long long timeout_ns;
+    uint32_t status[kStatusWords];   // [0]=code (0 ok), [1]=rank, [2]=block, [3]=stage, [4]=peer, [5]=expected, [6]=seen
+};
+
+enum StatusCode : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusSpinCap = 2 };
+
+// ---------------------------------------------------------------------------------------
+// 16-byte global memory access
+// ---------------------------------------------------------------------------------------
+// Streaming read of data that is read once (inputs, residual): evict-first.
+__device__ __forceinline__ uint4 ld_stream(const void *p) { return __ldcs(reinterpret_cast<const uint4 *>(p)); }
+// Read of staging memory that a peer GPU has written: served by L2, never by a stale L1 line.
+__device__ __forceinline__ uint4 ld_staging(const void *p) { return __ldcg(reinterpret_cast<const uint4 *>(p)); }
+// Read-mostly data with reuse across rows (RMSNorm weight).
+__device__ __forceinline__ uint4 ld_keep(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+__device__ __forceinline__ void st_stream(void *p, const uint4 &v) { __stcs(reinterpret_cast<uint4 *>(p), v); }
+// Store into memory that may live on a peer GPU (or locally): plain write-back store.
+__device__ __forceinline__ void st_peer(void *p, const uint4 &v) { *reinterpret_cast<uint4 *>(p) = v; }
+
+// ---------------------------------------------------------------------------------------
+// element traits: how 16 bytes unpack to fp32 lanes and round back
+// ---------------------------------------------------------------------------------------
+template <typename T>
+struct Elem;
+
+template <>
+struct Elem<__nv_bfloat16> {
+    static constexpr int kVec = 8;
+    __device__ static __forceinline__ void unpack(const uint4 &u, float (&f)[8]) {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // value of x after one round-to-nearest-even to the storage type
+    __device__ static __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+};
+
+template <>
+struct Elem<__half> {
+    static constexpr int kVec = 8;
+    __device__ static __forceinline__ void unpack(const uint4 &u, float (&f)[8]) {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            f[2 * i] = v.x;
+            f[2 * i + 1] = v.y;
+        }
+    }
+    __device__ static __forceinline__ uint4 pack(const float (&f)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+};
+
+template <>
+struct Elem<float> {
+    static constexpr int kVec = 4;
+    __device__ static __forceinline__ void unpack(const uint4 &u, float (&f)[4]) {
+        f[0] = __uint_as_float(u.x);
+        f[1] = __uint_as_float(u.y);
+        f[2] = __uint_as_float(u.z);
+        f[3] = __uint_as_float(u.w);
+    }
+    __device__ static __forceinline__ uint4 pack(const float (&f)[4]) {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    }
+    __device__ static __forceinline__ float round(float x) { return x; }
+};
+
+// ---------------------------------------------------------------------------------------
+// reductions: xor-shuffle inside a warp, one shared-memory hop across warps.  Every thread
+// of the block must call these (threads without data pass the identity).  `sm` holds 32
+// floats and must not be reused by another reduction before the next block-wide barrier.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float block_sum(float v, float *sm) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (nwarps == 1) return v;
+    if (lane == 0) sm[warp] = v;
+    __syncthreads();
+    v = lane < nwarps ? sm[lane] : 0.f;
+    return warp_sum(v);
+}
+__device__ __forceinline__ float block_max(float v, float *sm) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    if (nwarps == 1) return v;
+    if (lane == 0) sm[warp] = v;
+    __syncthreads();
+    v = lane < nwarps ? sm[lane] : 0.f;     // operands are magnitudes, so 0 is the identity
+    return warp_max(v);
+}
+
+// ---------------------------------------------------------------------------------------
+// fp32 -> FP8 e4m3, round to nearest even, saturating: one hardware instruction per pair
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// Four floats -> four FP8 bytes (little-endian lane order).  For the fnuz flavour the value
+// is doubled (e4m3fnuz has exponent bias 8 where e4m3fn has 7, so code_fnuz(x) == code_fn(2x))
+// and the negative-zero pattern 0x80, which fnuz reads as NaN, is folded to +0.
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d, int fnuz) {
+    if (fnuz) {
+        a += a; b += b; c += c; d += d;
+    }
+    uint32_t w = cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+    if (fnuz) {
+        // a byte equal to 0x80 becomes 0x00; every other byte is unchanged
+        uint32_t low7 = w & 0x7f7f7f7fu;
+        uint32_t nonzero7 = (low7 + 0x7f7f7f7fu) & 0x80808080u;   // bit 7 set where low 7 bits != 0
+        w = low7 | (w & nonzero7);
+    }
+    return w;
+}
+
+// ---------------------------------------------------------------------------------------
+// cross-GPU flags
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_release_sys(uint32_t *addr, uint32_t v) {
+    asm volatile("st.global.release.sys.b32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr) {
+    uint32_t v;
+    asm volatile("ld.global.acquire.sys.b32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t *addr) {
+    uint32_t v;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+constexpr uint32_t kSpinCap = 1u << 24;   // hard bound on polls of one wait, independent of the timer
+
+__device__ __forceinline__ void record_status(LocalState *st, uint32_t code, int rank, int block, int stage,
+                                              int peer, uint32_t expected, uint32_t seen) {
+    if (atomicCAS(&st->status[0], 0u, code) == 0u) {
+        st->status[1] = rank;
+        st->status[2] = block;
+        st->status[3] = stage;
+        st->status[4] = peer;
+        st->status[5] = expected;
+        st->status[6] = seen;
+    }
+    atomicExch(&st->abort, 1u);
+}
+
+// Poll `addr` (local memory that a peer writes) until it reaches `target` in wrap-safe order.
+// Gives up after the workspace's time budget or kSpinCap polls, records where, and returns
+// false; the caller carries on so that the kernel always terminates.
+__device__ __forceinline__ bool wait_flag(const uint32_t *addr, uint32_t target, LocalState *st, int rank,
+                                          int block, int stage, int peer) {
+    unsigned long long t0 = 0;
+    uint32_t seen = 0;
+    for (uint32_t it = 1; it <= kSpinCap; ++it) {
+        seen = ld_acquire_sys(addr);
+        if (static_cast<int32_t>(seen - target) >= 0) return true;
+        if ((it & 63u) == 0u) {
+            unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+                if (ld_volatile_u32(&st->abort)) break;
+            } else if (now - t0 > st->timeout_ns || ld_volatile_u32(&st->abort)) {
+                record_status(st, kStatusWaitTimeout, rank, block, stage, peer, target, seen);
+                return false;
+            }
+        }
+    }
+    record_status(st, kStatusSpinCap, rank, block, stage, peer, target, seen);
+    return false;
+}
+
+__host__ __device__ __forceinline__ size_t flag_index(int stage, int block, int src_rank) {
+    return (static_cast<size_t>(stage) * kMaxBlocks + block) * kMaxRanks + src_rank;
+}
+constexpr size_t kFlagBytes = sizeof(uint32_t) * kFlagStages * kMaxBlocks * kMaxRanks;
+
+}  // namespace gpuk

@@ -1,0 +1,708 @@
+// Host side of the C ABI declared in include/gpuk_b200.h: the per-rank workspace (staging
+// memory, flag array, device-resident state), CUDA-IPC export/import, the launch policy and
+// the entry points.  Replaces src/ops/all_reduce_fusion.cpp:4-396 of the reference.
+//
+// Workspace memory of one rank (one cudaMalloc, exported as one IPC handle):
+//
+//   [0, N*rs_slot)              two-shot reduce-scatter slots: slot s holds, for every row, the
+//                               column slice this rank owns as pushed by rank s
+//   [ag_off, ag_off + cap)      two-shot gather area: the reduced tensor, same layout as the input
+//   [os_off, os_off + 2*N*os)   one-shot slots, double-buffered by call parity: slot s of a
+//                               buffer holds rank s's whole message
+//
+// A second, small allocation holds the flags peers write (one row of N counters per CTA index
+// and stage).  The device-resident LocalState (epoch, ticket, status) is never exported.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <new>
+#include <string>
+#include <type_traits>
+#include <vector>
+
+#include "../../include/gpuk_b200.h"
+#include "launch.cuh"
+
+using namespace gpuk;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define GPUK_CUDA(expr)                                                                            \
+    do {                                                                                           \
+        cudaError_t err__ = (expr);                                                                \
+        if (err__ != cudaSuccess)                                                                  \
+            return fail(GPUK_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), \
+                        __FILE__, __LINE__);                                                       \
+    } while (0)
+
+constexpr int kDefaultSmCount = 148;            // B200
+constexpr int64_t kOneShotSlotBytes = 2 << 20;  // largest one-shot message
+constexpr int64_t kRsSlack = 1 << 20;           // room for ceil(row_vecs / N) rounding in the RS slots
+constexpr uint64_t kDefaultTimeoutNs = 2000000000ull;
+constexpr int kPlainRowVecs = 1024;             // the plain all-reduce views its input as 16 KiB rows
+
+int elem_size(int dtype) {
+    switch (dtype) {
+    case GPUK_DTYPE_BF16:
+    case GPUK_DTYPE_F16: return 2;
+    case GPUK_DTYPE_F32: return 4;
+    default: return 0;
+    }
+}
+
+bool valid_world(int w) { return w == 2 || w == 4 || w == 8; }
+
+int64_t default_oneshot_max_bytes(int world) {
+    // Starting point before measurement: reference rule impl.h:375-376 scaled up for NVLink 5.
+    switch (world) {
+    case 2: return 1 << 20;
+    case 4: return 512 << 10;
+    default: return 256 << 10;
+    }
+}
+
+bool quant_from_type(int quant_type, Quant *q) {
+    switch (quant_type) {
+    case GPUK_QUANT_NONE: *q = {kQuantNone, 0, 0.f}; return true;
+    case GPUK_QUANT_FP8_E4M3FN_240: *q = {kQuantDynamic, 0, 240.f}; return true;
+    case GPUK_QUANT_FP8_E4M3FNUZ_120: *q = {kQuantDynamic, 1, 120.f}; return true;
+    case GPUK_QUANT_FP8_E4M3FN_448: *q = {kQuantDynamic, 0, 448.f}; return true;
+    case GPUK_QUANT_FP8_E4M3FN_448_STATIC: *q = {kQuantStatic, 0, 448.f}; return true;
+    default: return false;
+    }
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int max_threads_for(int vpt) { return vpt >= 4 ? 512 : 1024; }
+
+// Tile of a row: `vpt` 16-byte vectors per thread, `threads` per CTA.
+bool pick_tile(int row_vecs, bool latency, int *vpt, int *threads) {
+    const int target = latency ? 1024 : 256;
+    int v = 1;
+    while (v < 8 && row_vecs > v * target) v *= 2;
+    while ((row_vecs + v - 1) / v > max_threads_for(v)) {
+        if (v == 8) return false;
+        v *= 2;
+    }
+    int t = (row_vecs + v - 1) / v;
+    t = (t + 31) / 32 * 32;
+    *vpt = v;
+    *threads = t;
+    return true;
+}
+
+}  // namespace
+
+struct gpuk_ws {
+    int device = 0, rank = 0, world = 0;
+    int sm_count = kDefaultSmCount;
+    int64_t cap = 0;            // largest message in bytes
+    int64_t rs_slot_bytes = 0, ag_off = 0, os_off = 0, os_slot_bytes = 0, data_bytes = 0;
+    char *data = nullptr;
+    uint32_t *flags = nullptr;
+    LocalState *st = nullptr;
+    ArParams *emul_params = nullptr;   // device scratch for the one-GPU emulation (lazily allocated)
+    void *peer_data[kMaxRanks] = {};
+    void *peer_flags[kMaxRanks] = {};
+    bool have_data = false, have_flags = false;
+    std::vector<void *> ipc_opened;
+    int64_t oneshot_max_bytes = 0;
+    std::map<uint32_t, int> occupancy;   // resident CTAs per SM, by kernel instantiation
+};
+
+extern "C" {
+
+const char *gpuk_last_error(void) { return g_last_error.c_str(); }
+
+const char *gpuk_status_string(int status) {
+    switch (status) {
+    case GPUK_OK: return "ok";
+    case GPUK_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case GPUK_ERR_CUDA: return "CUDA runtime error";
+    case GPUK_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case GPUK_ERR_NOT_READY: return "peer memory not opened";
+    case GPUK_ERR_TOO_LARGE: return "message larger than the workspace";
+    case GPUK_ERR_PEER_TIMEOUT: return "timed out waiting for a peer";
+    default: return "unknown status";
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// planning (pure host arithmetic)
+// ---------------------------------------------------------------------------------------
+int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype, int sm_count,
+                            int ctas_per_sm_limit, int64_t oneshot_max_bytes, gpuk_plan *out) {
+    if (!out) return fail(GPUK_ERR_INVALID_ARGUMENT, "plan: out is null");
+    const int es = elem_size(dtype);
+    if (!es) return fail(GPUK_ERR_UNSUPPORTED, "plan: unknown dtype %d", dtype);
+    if (world_size != 1 && !valid_world(world_size))
+        return fail(GPUK_ERR_INVALID_ARGUMENT, "plan: world size %d is not 1, 2, 4 or 8", world_size);
+    if (numel < 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "plan: negative numel");
+    if (sm_count <= 0) sm_count = kDefaultSmCount;
+    const int kv = 16 / es;
+    const bool fused = hidden > 0;
+    int row_vecs;
+    int64_t rows;
+    if (fused) {
+        if (hidden % kv) return fail(GPUK_ERR_UNSUPPORTED, "hidden %d is not a multiple of %d elements (16 bytes)", hidden, kv);
+        if (numel % hidden) return fail(GPUK_ERR_INVALID_ARGUMENT, "numel %lld is not a multiple of hidden %d", (long long)numel, hidden);
+        row_vecs = hidden / kv;
+        rows = numel / hidden;
+    } else {
+        if (numel % kv) return fail(GPUK_ERR_UNSUPPORTED, "numel %lld is not a multiple of %d elements (16 bytes)", (long long)numel, kv);
+        const int64_t total_vecs = numel / kv;
+        row_vecs = static_cast<int>(std::min<int64_t>(std::max<int64_t>(total_vecs, 1), kPlainRowVecs));
+        rows = (total_vecs + row_vecs - 1) / row_vecs;
+    }
+    if (rows > (1ll << 30)) return fail(GPUK_ERR_UNSUPPORTED, "too many rows");
+    const int64_t bytes = numel * es;
+    if (oneshot_max_bytes <= 0) oneshot_max_bytes = world_size > 1 ? default_oneshot_max_bytes(world_size) : 0;
+    const bool one_shot = world_size > 1 && bytes <= std::min(oneshot_max_bytes, kOneShotSlotBytes) && rows <= kMaxBlocks;
+    const bool latency = rows <= sm_count;
+    int vpt = 4, threads = 256;
+    if (fused || one_shot) {
+        if (!pick_tile(row_vecs, latency, &vpt, &threads))
+            return fail(GPUK_ERR_UNSUPPORTED, "row of %d vectors is longer than the largest tile", row_vecs);
+        if (!fused) { vpt = 4; threads = std::max(32, ((row_vecs + 3) / 4 + 31) / 32 * 32); }
+    }
+    int per_sm = std::max(1, std::min(4, 1024 / threads));
+    if (ctas_per_sm_limit > 0) per_sm = std::min(per_sm, ctas_per_sm_limit);
+    const int64_t cta_cap = std::min<int64_t>(static_cast<int64_t>(sm_count) * per_sm, kMaxBlocks);
+    int rpc = 1;
+    if (world_size > 1 && !one_shot) {
+        const int vpr = (row_vecs + world_size - 1) / world_size;
+        if (rows > cta_cap) rpc = std::max(1, std::min(4, (threads + vpr - 1) / vpr));
+    }
+    const int64_t nchunks = (rows + rpc - 1) / rpc;
+    int64_t grid;
+    if (world_size == 1) grid = std::min<int64_t>(rows, static_cast<int64_t>(sm_count) * 8);
+    else grid = std::min<int64_t>(nchunks, cta_cap);
+    out->one_shot = one_shot ? 1 : 0;
+    out->vpt = vpt;
+    out->threads = threads;
+    out->rows_per_chunk = rpc;
+    out->grid = static_cast<int>(std::max<int64_t>(grid, 0));
+    out->rows = static_cast<int>(rows);
+    out->row_vecs = row_vecs;
+    out->message_bytes = bytes;
+    return GPUK_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// workspace
+// ---------------------------------------------------------------------------------------
+int gpuk_ws_create(int device_id, int rank, int world_size, int64_t max_size_in_bytes,
+                   int64_t comm_ptrs_buf_len, gpuk_ws **out) {
+    (void)comm_ptrs_buf_len;
+    if (!out) return fail(GPUK_ERR_INVALID_ARGUMENT, "ws_create: out is null");
+    *out = nullptr;
+    if (!valid_world(world_size)) return fail(GPUK_ERR_INVALID_ARGUMENT, "world size is not supported");
+    if (rank < 0 || rank >= world_size) return fail(GPUK_ERR_INVALID_ARGUMENT, "invalid rank passed in");
+    if (max_size_in_bytes <= 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "max_size_in_bytes must be positive");
+    if (device_id < 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "invalid device id");
+    GPUK_CUDA(cudaSetDevice(device_id));
+    gpuk_ws *ws = new (std::nothrow) gpuk_ws();
+    if (!ws) return fail(GPUK_ERR_CUDA, "out of host memory");
+    ws->device = device_id;
+    ws->rank = rank;
+    ws->world = world_size;
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_id) == cudaSuccess && sms > 0) ws->sm_count = sms;
+    const int64_t align = 256ll * world_size;
+    ws->cap = (max_size_in_bytes + align - 1) / align * align;
+    ws->rs_slot_bytes = ws->cap / world_size + kRsSlack;
+    ws->ag_off = ws->rs_slot_bytes * world_size;
+    ws->os_off = ws->ag_off + ws->cap;
+    ws->os_slot_bytes = std::min<int64_t>(ws->cap, kOneShotSlotBytes);
+    ws->data_bytes = ws->os_off + 2 * world_size * ws->os_slot_bytes;
+    cudaError_t e = cudaMalloc(&ws->data, ws->data_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ws->flags, kFlagBytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ws->st, sizeof(LocalState));
+    if (e == cudaSuccess) e = cudaMemset(ws->flags, 0, kFlagBytes);
+    if (e == cudaSuccess) {
+        LocalState init;
+        memset(&init, 0, sizeof(init));
+        init.timeout_ns = kDefaultTimeoutNs;
+        e = cudaMemcpy(ws->st, &init, sizeof(init), cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+        cudaFree(ws->data);
+        cudaFree(ws->flags);
+        cudaFree(ws->st);
+        delete ws;
+        return fail(GPUK_ERR_CUDA, "workspace allocation failed: %s", cudaGetErrorString(e));
+    }
+    ws->peer_data[rank] = ws->data;
+    ws->peer_flags[rank] = ws->flags;
+    *out = ws;
+    return GPUK_OK;
+}
+
+int gpuk_ws_destroy(gpuk_ws *ws) {
+    if (!ws) return GPUK_OK;
+    cudaSetDevice(ws->device);
+    cudaDeviceSynchronize();
+    for (void *p : ws->ipc_opened) cudaIpcCloseMemHandle(p);
+    cudaFree(ws->data);
+    cudaFree(ws->flags);
+    cudaFree(ws->st);
+    cudaFree(ws->emul_params);
+    delete ws;
+    return GPUK_OK;
+}
+
+static int export_handle(gpuk_ws *ws, void *ptr, uint8_t *out) {
+    if (!ws || !out) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace or output");
+    static_assert(sizeof(cudaIpcMemHandle_t) == GPUK_IPC_HANDLE_BYTES, "IPC handle size");
+    GPUK_CUDA(cudaSetDevice(ws->device));
+    cudaIpcMemHandle_t h;
+    GPUK_CUDA(cudaIpcGetMemHandle(&h, ptr));
+    memcpy(out, &h, sizeof(h));
+    return GPUK_OK;
+}
+
+int gpuk_ws_get_barrier_handle(gpuk_ws *ws, uint8_t out[GPUK_IPC_HANDLE_BYTES]) {
+    return export_handle(ws, ws ? ws->flags : nullptr, out);
+}
+int gpuk_ws_get_data_handle(gpuk_ws *ws, uint8_t out[GPUK_IPC_HANDLE_BYTES]) {
+    return export_handle(ws, ws ? ws->data : nullptr, out);
+}
+
+static int open_handles(gpuk_ws *ws, const uint8_t *handles, int n, void **table, bool *ready) {
+    if (!ws || !handles) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace or handles");
+    if (n != ws->world) return fail(GPUK_ERR_INVALID_ARGUMENT, "expected %d handles, got %d", ws->world, n);
+    GPUK_CUDA(cudaSetDevice(ws->device));
+    for (int r = 0; r < n; ++r) {
+        if (r == ws->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + static_cast<size_t>(r) * GPUK_IPC_HANDLE_BYTES, sizeof(h));
+        void *p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fail(GPUK_ERR_CUDA, "cudaIpcOpenMemHandle for rank %d failed: %s", r, cudaGetErrorString(e));
+        }
+        table[r] = p;
+        ws->ipc_opened.push_back(p);
+    }
+    *ready = true;
+    return GPUK_OK;
+}
+
+int gpuk_ws_open_barrier_handles(gpuk_ws *ws, const uint8_t *handles, int n) {
+    return open_handles(ws, handles, n, ws ? ws->peer_flags : nullptr, ws ? &ws->have_flags : nullptr);
+}
+int gpuk_ws_open_data_handles(gpuk_ws *ws, const uint8_t *handles, int n) {
+    return open_handles(ws, handles, n, ws ? ws->peer_data : nullptr, ws ? &ws->have_data : nullptr);
+}
+
+int gpuk_ws_local_pointers(gpuk_ws *ws, void **flags, void **data) {
+    if (!ws || !flags || !data) return fail(GPUK_ERR_INVALID_ARGUMENT, "null argument");
+    *flags = ws->flags;
+    *data = ws->data;
+    return GPUK_OK;
+}
+
+int gpuk_ws_set_peer_pointers(gpuk_ws *ws, void *const *flags, void *const *data, int n) {
+    if (!ws || !flags || !data) return fail(GPUK_ERR_INVALID_ARGUMENT, "null argument");
+    if (n != ws->world) return fail(GPUK_ERR_INVALID_ARGUMENT, "expected %d pointers, got %d", ws->world, n);
+    for (int r = 0; r < n; ++r) {
+        if (!flags[r] || !data[r]) return fail(GPUK_ERR_INVALID_ARGUMENT, "null peer pointer for rank %d", r);
+        if (r == ws->rank) continue;
+        ws->peer_flags[r] = flags[r];
+        ws->peer_data[r] = data[r];
+    }
+    ws->have_flags = ws->have_data = true;
+    return GPUK_OK;
+}
+
+int gpuk_enable_peer_access(int n_devices) {
+    int count = 0;
+    GPUK_CUDA(cudaGetDeviceCount(&count));
+    if (n_devices <= 0 || n_devices > count) return fail(GPUK_ERR_INVALID_ARGUMENT, "%d devices requested, %d present", n_devices, count);
+    int prev = 0;
+    GPUK_CUDA(cudaGetDevice(&prev));
+    for (int a = 0; a < n_devices; ++a) {
+        GPUK_CUDA(cudaSetDevice(a));
+        for (int b = 0; b < n_devices; ++b) {
+            if (a == b) continue;
+            int can = 0;
+            GPUK_CUDA(cudaDeviceCanAccessPeer(&can, a, b));
+            if (!can) return fail(GPUK_ERR_UNSUPPORTED, "device %d cannot access device %d", a, b);
+            cudaError_t e = cudaDeviceEnablePeerAccess(b, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else if (e != cudaSuccess) return fail(GPUK_ERR_CUDA, "cudaDeviceEnablePeerAccess(%d->%d): %s", a, b, cudaGetErrorString(e));
+        }
+    }
+    GPUK_CUDA(cudaSetDevice(prev));
+    return GPUK_OK;
+}
+
+// ---- capture-registration surface: nothing to register in a push design ------------------
+int gpuk_ws_capture_clear(gpuk_ws *ws) {
+    if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
+    return GPUK_OK;
+}
+int gpuk_ws_captured_count(gpuk_ws *ws, int *count) {
+    if (!ws || !count) return fail(GPUK_ERR_INVALID_ARGUMENT, "null argument");
+    *count = 0;
+    return GPUK_OK;
+}
+int gpuk_ws_open_captured_handles(gpuk_ws *ws, const uint8_t *handles, const int64_t *offsets, int n, int64_t ptr_idx) {
+    (void)handles; (void)offsets; (void)n;
+    if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
+    return fail(GPUK_ERR_INVALID_ARGUMENT, "no captured tensor with index %lld: captured calls need no registration", (long long)ptr_idx);
+}
+
+static int base_of(const void *ptr, void **base) {
+    if (!ptr) return fail(GPUK_ERR_INVALID_ARGUMENT, "null pointer");
+    // the driver entry point is looked up at run time so that this library loads without libcuda
+    typedef CUresult (*PointerGetAttribute)(void *, CUpointer_attribute, CUdeviceptr);
+    static PointerGetAttribute get_attr = nullptr;
+    if (!get_attr) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        cudaError_t e = cudaGetDriverEntryPoint("cuPointerGetAttribute", &fn, cudaEnableDefault, &qr);
+        if (e != cudaSuccess || !fn) {
+            cudaGetLastError();
+            return fail(GPUK_ERR_CUDA, "cuPointerGetAttribute is not available");
+        }
+        get_attr = reinterpret_cast<PointerGetAttribute>(fn);
+    }
+    CUdeviceptr b = 0;
+    CUresult r = get_attr(&b, CU_POINTER_ATTRIBUTE_RANGE_START_ADDR, reinterpret_cast<CUdeviceptr>(ptr));
+    if (r != CUDA_SUCCESS) return fail(GPUK_ERR_CUDA, "failed to get pointer attr");
+    *base = reinterpret_cast<void *>(b);
+    return GPUK_OK;
+}
+int gpuk_tensor_ipc_handle(const void *ptr, uint8_t out[GPUK_IPC_HANDLE_BYTES]) {
+    if (!out) return fail(GPUK_ERR_INVALID_ARGUMENT, "null output");
+    void *base = nullptr;
+    int rc = base_of(ptr, &base);
+    if (rc) return rc;
+    cudaIpcMemHandle_t h;
+    GPUK_CUDA(cudaIpcGetMemHandle(&h, base));
+    memcpy(out, &h, sizeof(h));
+    return GPUK_OK;
+}
+int gpuk_tensor_ipc_offset(const void *ptr, int64_t *offset) {
+    if (!offset) return fail(GPUK_ERR_INVALID_ARGUMENT, "null output");
+    void *base = nullptr;
+    int rc = base_of(ptr, &base);
+    if (rc) return rc;
+    *offset = reinterpret_cast<const char *>(ptr) - reinterpret_cast<const char *>(base);
+    return GPUK_OK;
+}
+
+// ---- knobs and status --------------------------------------------------------------------
+int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes) {
+    if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
+    ws->oneshot_max_bytes = bytes > 0 ? bytes : 0;
+    return GPUK_OK;
+}
+int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns) {
+    if (!ws || ns == 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace or zero budget");
+    GPUK_CUDA(cudaSetDevice(ws->device));
+    unsigned long long v = ns;
+    GPUK_CUDA(cudaMemcpy(&ws->st->timeout_ns, &v, sizeof(v), cudaMemcpyHostToDevice));
+    return GPUK_OK;
+}
+int gpuk_ws_status(gpuk_ws *ws, uint32_t out[8]) {
+    if (!ws || !out) return fail(GPUK_ERR_INVALID_ARGUMENT, "null argument");
+    GPUK_CUDA(cudaSetDevice(ws->device));
+    GPUK_CUDA(cudaDeviceSynchronize());
+    LocalState host;
+    GPUK_CUDA(cudaMemcpy(&host, ws->st, sizeof(host), cudaMemcpyDeviceToHost));
+    memcpy(out, host.status, sizeof(host.status));
+    if (out[0] != 0)
+        return fail(GPUK_ERR_PEER_TIMEOUT, "rank %u CTA %u stage %u gave up waiting for rank %u (expected flag %u, saw %u)",
+                    out[1], out[2], out[3], out[4], out[5], out[6]);
+    return GPUK_OK;
+}
+int gpuk_ws_clear_status(gpuk_ws *ws) {
+    if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
+    GPUK_CUDA(cudaSetDevice(ws->device));
+    GPUK_CUDA(cudaDeviceSynchronize());
+    GPUK_CUDA(cudaMemset(ws->st->status, 0, sizeof(uint32_t) * kStatusWords));
+    GPUK_CUDA(cudaMemset(&ws->st->abort, 0, sizeof(uint32_t)));
+    return GPUK_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// kernels launched from this file
+// ---------------------------------------------------------------------------------------
+namespace {
+
+__global__ void selftest_wait_kernel(LocalState *st, const uint32_t *flag, int rank) {
+    if (threadIdx.x == 0) wait_flag(flag, ld_volatile_u32(flag) + 1u, st, rank, 0, 0, rank);
+}
+
+template <typename F>
+int by_dtype(int dtype, F &&f) {
+    switch (dtype) {
+    case GPUK_DTYPE_BF16: return f(static_cast<__nv_bfloat16 *>(nullptr));
+    case GPUK_DTYPE_F16: return f(static_cast<__half *>(nullptr));
+    case GPUK_DTYPE_F32: return f(static_cast<float *>(nullptr));
+    default: return fail(GPUK_ERR_UNSUPPORTED, "unknown dtype %d", dtype);
+    }
+}
+
+struct CallArgs {
+    const void *in;
+    const void *residual;
+    const void *gamma;
+    void *residual_out;
+    void *norm_out;
+    float *scale_out;
+    int64_t numel;
+    int hidden;      // 0: plain all-reduce (in place over `in`)
+    int dtype;
+    float eps;
+    int quant_type;
+};
+
+int check_fused_args(const CallArgs &a, Quant *q) {
+    if (!quant_from_type(a.quant_type, q)) return fail(GPUK_ERR_INVALID_ARGUMENT, "unknown quant_type %d", a.quant_type);
+    if (!a.in || !a.residual || !a.gamma || !a.residual_out || !a.norm_out)
+        return fail(GPUK_ERR_INVALID_ARGUMENT, "null tensor pointer");
+    if (q->mode != kQuantNone && !a.scale_out) return fail(GPUK_ERR_INVALID_ARGUMENT, "scale_out is null");
+    if (!aligned16(a.in) || !aligned16(a.residual) || !aligned16(a.gamma) || !aligned16(a.residual_out) || !aligned16(a.norm_out))
+        return fail(GPUK_ERR_INVALID_ARGUMENT, "tensor pointers must be 16-byte aligned");
+    if (a.hidden <= 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "hidden must be positive");
+    return GPUK_OK;
+}
+
+void fill_epilogue(const CallArgs &a, const Quant &q, int row_vecs, EpilogueArgs *ep) {
+    ep->residual = a.residual;
+    ep->gamma = a.gamma;
+    ep->residual_out = a.residual_out;
+    ep->norm_out = a.norm_out;
+    ep->scale_out = a.scale_out;
+    ep->hidden = a.hidden;
+    ep->row_vecs = row_vecs;
+    ep->eps = a.eps;
+    ep->q = q;
+}
+
+// Fills the parameter block of one rank and the launch shape shared by all ranks.
+int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated, ArParams *p, ArShape *shape) {
+    if (!ws->have_data || !ws->have_flags) return fail(GPUK_ERR_NOT_READY, "peer handles have not been opened");
+    const bool fused = a.hidden > 0;
+    Quant q = {kQuantNone, 0, 0.f};
+    if (fused) {
+        int rc = check_fused_args(a, &q);
+        if (rc) return rc;
+    } else {
+        if (!a.in) return fail(GPUK_ERR_INVALID_ARGUMENT, "null tensor pointer");
+        if (!aligned16(a.in)) return fail(GPUK_ERR_INVALID_ARGUMENT, "tensor pointers must be 16-byte aligned");
+    }
+    gpuk_plan plan;
+    int rc = gpuk_plan_allreduce_rms(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, ws->oneshot_max_bytes, &plan);
+    if (rc) return rc;
+    if (plan.message_bytes > ws->cap)
+        return fail(GPUK_ERR_TOO_LARGE, "message of %lld bytes exceeds the workspace (%lld bytes)",
+                    (long long)plan.message_bytes, (long long)ws->cap);
+    bool one_shot = plan.one_shot != 0;
+    if (force_mode == 1) {
+        if (plan.message_bytes > ws->os_slot_bytes || plan.rows > kMaxBlocks)
+            return fail(GPUK_ERR_TOO_LARGE, "message too large for the one-shot path");
+        one_shot = true;
+    } else if (force_mode == 2) {
+        one_shot = false;
+    }
+    if (one_shot != (plan.one_shot != 0)) {
+        // re-plan with the crossover forced to the requested side
+        rc = gpuk_plan_allreduce_rms(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0,
+                                     one_shot ? kOneShotSlotBytes : 1, &plan);
+        if (rc) return rc;
+        if ((plan.one_shot != 0) != one_shot) return fail(GPUK_ERR_UNSUPPORTED, "requested exchange mode is not available for this shape");
+    }
+    const int es = elem_size(a.dtype);
+    memset(p, 0, sizeof(*p));
+    p->in = a.in;
+    p->out = const_cast<void *>(a.in);
+    p->total_vecs = a.numel * es / 16;
+    p->rows = plan.rows;
+    p->row_vecs = plan.row_vecs;
+    p->rows_per_chunk = plan.rows_per_chunk;
+    if (fused) fill_epilogue(a, q, plan.row_vecs, &p->ep);
+    p->rank = ws->rank;
+    p->vpr = (plan.row_vecs + ws->world - 1) / ws->world;
+    for (int r = 0; r < ws->world; ++r) {
+        p->peer_data[r] = static_cast<char *>(ws->peer_data[r]);
+        p->peer_flags[r] = static_cast<uint32_t *>(ws->peer_flags[r]);
+    }
+    p->st = ws->st;
+    p->rs_slot_bytes = ws->rs_slot_bytes;
+    p->ag_off = ws->ag_off;
+    p->os_off = ws->os_off;
+    p->os_slot_bytes = ws->os_slot_bytes;
+    if (!one_shot && static_cast<int64_t>(plan.rows) * p->vpr * 16 > ws->rs_slot_bytes)
+        return fail(GPUK_ERR_TOO_LARGE, "message does not fit the reduce-scatter slots of the workspace");
+
+    shape->world = ws->world;
+    shape->vpt = plan.vpt;
+    shape->two_shot = !one_shot;
+    shape->fused = fused;
+    shape->threads = plan.threads;
+    // the grid must be co-resident: CTAs of equal index on different ranks wait for each other
+    const uint32_t key = static_cast<uint32_t>(a.dtype) | (plan.vpt << 4) | (one_shot ? 1u << 8 : 0u) |
+                         (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (static_cast<uint32_t>(plan.threads) << 12);
+    int per_sm = 0;
+    auto cached = ws->occupancy.find(key);
+    if (cached != ws->occupancy.end()) {
+        per_sm = cached->second;
+    } else {
+        rc = by_dtype(a.dtype, [&](auto *t) {
+            using T = std::remove_pointer_t<decltype(t)>;
+            cudaError_t e = ar_blocks_per_sm<T>(*shape, emulated, &per_sm);
+            if (e != cudaSuccess || per_sm <= 0) {
+                cudaGetLastError();
+                return fail(GPUK_ERR_CUDA, "occupancy query failed for the selected kernel: %s", cudaGetErrorString(e));
+            }
+            return static_cast<int>(GPUK_OK);
+        });
+        if (rc) return rc;
+        ws->occupancy[key] = per_sm;
+    }
+    int64_t resident = static_cast<int64_t>(per_sm) * ws->sm_count;
+    if (emulated) resident /= ws->world;
+    const int64_t nchunks = (static_cast<int64_t>(plan.rows) + plan.rows_per_chunk - 1) / plan.rows_per_chunk;
+    int64_t grid = std::min<int64_t>(std::min<int64_t>(plan.grid, resident), nchunks);
+    if (grid < 1) grid = 1;
+    shape->grid = static_cast<int>(grid);
+    p->epoch_advance = static_cast<uint32_t>((nchunks + grid - 1) / grid + 1);
+    return GPUK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gpuk_ws_selftest_wait(gpuk_ws *ws, void *stream) {
+    if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
+    GPUK_CUDA(cudaSetDevice(ws->device));
+    // the flag of (stage 1, last CTA index, own rank) is never written by any kernel
+    const uint32_t *flag = ws->flags + flag_index(1, kMaxBlocks - 1, ws->rank);
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ws->st, flag, ws->rank);
+    GPUK_CUDA(cudaGetLastError());
+    return GPUK_OK;
+}
+
+int gpuk_residual_rms_quant(const void *in, const void *residual_in, const void *rms_gamma,
+                            void *residual_out, void *norm_out, float *scale_out, int64_t numel,
+                            int hidden, int dtype, float eps, int quant_type, void *stream) {
+    CallArgs a = {in, residual_in, rms_gamma, residual_out, norm_out, scale_out, numel, hidden, dtype, eps, quant_type};
+    Quant q;
+    if (numel == 0) return GPUK_OK;
+    int rc = check_fused_args(a, &q);
+    if (rc) return rc;
+    int device = 0, sms = kDefaultSmCount;
+    GPUK_CUDA(cudaGetDevice(&device));
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    gpuk_plan plan;
+    rc = gpuk_plan_allreduce_rms(1, numel, hidden, dtype, sms, 0, 0, &plan);
+    if (rc) return rc;
+    if (plan.rows == 0) return GPUK_OK;
+    NormQuantParams p;
+    memset(&p, 0, sizeof(p));
+    p.in = in;
+    p.rows = plan.rows;
+    fill_epilogue(a, q, plan.row_vecs, &p.ep);
+    return by_dtype(dtype, [&](auto *t) {
+        using T = std::remove_pointer_t<decltype(t)>;
+        cudaError_t e = launch_norm_quant<T>(p, plan.vpt, plan.threads, plan.grid, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(GPUK_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+        return static_cast<int>(GPUK_OK);
+    });
+}
+
+static int run_ar(gpuk_ws *ws, const CallArgs &a, void *stream) {
+    if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
+    if (a.numel == 0) return GPUK_OK;
+    GPUK_CUDA(cudaSetDevice(ws->device));
+    ArParams p;
+    ArShape shape;
+    int rc = build_ar_call(ws, a, 0, false, &p, &shape);
+    if (rc) return rc;
+    return by_dtype(a.dtype, [&](auto *t) {
+        using T = std::remove_pointer_t<decltype(t)>;
+        cudaError_t e = launch_ar<T>(p, shape, static_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) return fail(GPUK_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+        return static_cast<int>(GPUK_OK);
+    });
+}
+
+int gpuk_allreduce_rms(gpuk_ws *ws, const void *allreduce_in, const void *residual_in,
+                       const void *rms_gamma, void *residual_out, void *norm_out, float *scale_out,
+                       int64_t numel, int hidden, int dtype, float eps, int quant_type, void *stream) {
+    if (hidden <= 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "hidden must be positive");
+    CallArgs a = {allreduce_in, residual_in, rms_gamma, residual_out, norm_out, scale_out, numel, hidden, dtype, eps, quant_type};
+    return run_ar(ws, a, stream);
+}
+
+int gpuk_allreduce_inplace(gpuk_ws *ws, void *data, int64_t numel, int dtype, void *stream) {
+    CallArgs a = {data, nullptr, nullptr, nullptr, nullptr, nullptr, numel, 0, dtype, 0.f, 0};
+    return run_ar(ws, a, stream);
+}
+
+int gpuk_emulated_allreduce_rms(gpuk_ws *const *wss, int world_size, void *const *allreduce_in,
+                                const void *residual_in, const void *rms_gamma, void *const *residual_out,
+                                void *const *norm_out, float *const *scale_out, int64_t numel, int hidden,
+                                int dtype, float eps, int quant_type, int force_mode, void *stream) {
+    if (!wss || !allreduce_in) return fail(GPUK_ERR_INVALID_ARGUMENT, "null argument");
+    if (!valid_world(world_size)) return fail(GPUK_ERR_INVALID_ARGUMENT, "world size is not supported");
+    if (numel == 0) return GPUK_OK;
+    const bool fused = hidden > 0;
+    if (fused && (!residual_out || !norm_out)) return fail(GPUK_ERR_INVALID_ARGUMENT, "null output arrays");
+    ArParams host_params[kMaxRanks];
+    ArShape shape = {};
+    for (int r = 0; r < world_size; ++r) {
+        gpuk_ws *ws = wss[r];
+        if (!ws || ws->world != world_size || ws->rank != r || ws->device != wss[0]->device)
+            return fail(GPUK_ERR_INVALID_ARGUMENT, "workspace %d does not belong to this emulated group", r);
+        CallArgs a = {allreduce_in[r], residual_in, rms_gamma, fused ? residual_out[r] : nullptr,
+                      fused ? norm_out[r] : nullptr, (fused && scale_out) ? scale_out[r] : nullptr,
+                      numel, hidden, dtype, eps, quant_type};
+        ArShape s;
+        int rc = build_ar_call(ws, a, force_mode, true, &host_params[r], &s);
+        if (rc) return rc;
+        if (r == 0) shape = s;
+        else if (s.grid != shape.grid || s.threads != shape.threads || s.vpt != shape.vpt || s.two_shot != shape.two_shot)
+            return fail(GPUK_ERR_INVALID_ARGUMENT, "ranks disagree on the launch shape");
+    }
+    gpuk_ws *w0 = wss[0];
+    GPUK_CUDA(cudaSetDevice(w0->device));
+    if (!w0->emul_params) GPUK_CUDA(cudaMalloc(&w0->emul_params, sizeof(ArParams) * kMaxRanks));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    GPUK_CUDA(cudaMemcpyAsync(w0->emul_params, host_params, sizeof(ArParams) * world_size, cudaMemcpyHostToDevice, s));
+    GPUK_CUDA(cudaStreamSynchronize(s));   // host_params lives on this stack frame
+    return by_dtype(dtype, [&](auto *t) {
+        using T = std::remove_pointer_t<decltype(t)>;
+        cudaError_t e = launch_ar_emulated<T>(w0->emul_params, shape, s);
+        if (e != cudaSuccess) return fail(GPUK_ERR_CUDA, "cooperative launch failed: %s", cudaGetErrorString(e));
+        return static_cast<int>(GPUK_OK);
+    });
+}
+
+}  // extern "C"

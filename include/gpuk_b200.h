@@ -1,0 +1,237 @@
+/*
+ * gpuk_b200 -- C ABI of the B200-native tensor-parallel epilogue
+ * (all-reduce of per-rank partials + residual add + RMSNorm + FP8-e4m3 quantisation).
+ *
+ * Every entry point takes plain pointers and sizes, returns an int status (0 = success,
+ * never throws, never aborts) and enqueues its GPU work on the CUDA stream it is given.
+ * This is the boundary a binding for the reference's operator API links against; each
+ * declaration names the reference interface it stands in for (paths are relative to the
+ * reference project xytpai/gpuk).
+ *
+ * Threading: a workspace is not thread-safe and belongs to one process and one device
+ * (same contract as the reference's CommWorkspace, src/ops/all_reduce_fusion.cpp:44-254).
+ * All ranks of a group must issue the same sequence of collective calls with the same
+ * shapes.  Calls on one workspace must be ordered on one stream.
+ */
+#ifndef GPUK_B200_H_
+#define GPUK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GPUK_IPC_HANDLE_BYTES 64 /* sizeof(cudaIpcMemHandle_t) */
+#define GPUK_MAX_RANKS 8         /* src/common/communicator.h:57 */
+
+/* status codes */
+enum {
+    GPUK_OK = 0,
+    GPUK_ERR_INVALID_ARGUMENT = 1, /* bad rank / world size / null pointer / misaligned pointer */
+    GPUK_ERR_CUDA = 2,             /* a CUDA runtime call failed; see gpuk_last_error() */
+    GPUK_ERR_UNSUPPORTED = 3,      /* shape or dtype outside what the kernels cover */
+    GPUK_ERR_NOT_READY = 4,        /* peers' memory has not been opened yet */
+    GPUK_ERR_TOO_LARGE = 5,        /* message exceeds the workspace created by gpuk_ws_create */
+    GPUK_ERR_PEER_TIMEOUT = 6      /* a device-side wait for a peer ran out (gpuk_ws_status) */
+};
+
+/* element types of the activations */
+enum { GPUK_DTYPE_BF16 = 0, GPUK_DTYPE_F16 = 1, GPUK_DTYPE_F32 = 2 };
+
+/*
+ * quant_type of the fused operator.  0..2 keep the reference's meaning
+ * (src/impl/all_reduce_fusion_impl.h:13-17, saturation values src/common/float8.h:216-218
+ * and :249-251); 3 and 4 are additive.
+ */
+enum {
+    GPUK_QUANT_NONE = 0,               /* norm_out has the input dtype */
+    GPUK_QUANT_FP8_E4M3FN_240 = 1,     /* per-token dynamic scale = amax/240, e4m3fn codes */
+    GPUK_QUANT_FP8_E4M3FNUZ_120 = 2,   /* per-token dynamic scale = amax/120, e4m3fnuz codes */
+    GPUK_QUANT_FP8_E4M3FN_448 = 3,     /* per-token dynamic scale = amax/448, e4m3fn codes */
+    GPUK_QUANT_FP8_E4M3FN_448_STATIC = 4 /* one caller-supplied scale: scale_out[0] is READ */
+};
+
+typedef struct gpuk_ws gpuk_ws; /* opaque; the reference passes it around as an int64 "fptr" */
+
+/* Text of the most recent failure on the calling thread ("" if none). */
+const char *gpuk_last_error(void);
+const char *gpuk_status_string(int status);
+
+/* ------------------------------------------------------------------------------------- */
+/* workspace life cycle                                                                  */
+/* ------------------------------------------------------------------------------------- */
+
+/*
+ * Replaces init_ar_fusion (src/register.cpp:5-6, src/ops/all_reduce_fusion.cpp:256-268) and
+ * the CommWorkspace constructor (:46-70).  world_size must be 2, 4 or 8 and
+ * 0 <= rank < world_size, otherwise GPUK_ERR_INVALID_ARGUMENT (the reference throws
+ * std::invalid_argument).  max_size_in_bytes is the largest message (bytes of one rank's
+ * input) the workspace must carry.  comm_ptrs_buf_len is accepted for signature
+ * compatibility and ignored: no pointer table is needed because peers never read inputs.
+ * Argument validation happens before any CUDA call.
+ */
+int gpuk_ws_create(int device_id, int rank, int world_size, int64_t max_size_in_bytes,
+                   int64_t comm_ptrs_buf_len, gpuk_ws **out);
+
+/* Replaces destroy_ar_fusion (src/register.cpp:7-8, all_reduce_fusion.cpp:270-273). */
+int gpuk_ws_destroy(gpuk_ws *ws);
+
+/*
+ * Replace get_ar_fusion_barrier_handle / get_ar_fusion_data_handle (src/register.cpp:10-13,
+ * all_reduce_fusion.cpp:275-283): write the 64-byte cudaIpcMemHandle_t of the flag array /
+ * of the staging memory to `out`.
+ */
+int gpuk_ws_get_barrier_handle(gpuk_ws *ws, uint8_t out[GPUK_IPC_HANDLE_BYTES]);
+int gpuk_ws_get_data_handle(gpuk_ws *ws, uint8_t out[GPUK_IPC_HANDLE_BYTES]);
+
+/*
+ * Replace open_ar_fusion_barrier_handles / open_ar_fusion_data_handles (src/register.cpp:15-18,
+ * all_reduce_fusion.cpp:285-293, ipc_details::open_handles :15-34).  `handles` holds
+ * world_size consecutive 64-byte handles in rank order; the entry of this rank is ignored.
+ */
+int gpuk_ws_open_barrier_handles(gpuk_ws *ws, const uint8_t *handles, int n);
+int gpuk_ws_open_data_handles(gpuk_ws *ws, const uint8_t *handles, int n);
+
+/*
+ * Single-process alternative to the IPC exchange, for a process that owns all GPUs and has
+ * enabled peer access itself -- the harness style of the reference's C++ tests
+ * (test/cpp/test_all_reduce.cpp:337-356 with src/common/communicator.h:40-55).
+ * gpuk_ws_local_pointers returns this rank's flag array and staging base;
+ * gpuk_ws_set_peer_pointers installs all ranks' pointers (rank order) on this workspace.
+ */
+int gpuk_ws_local_pointers(gpuk_ws *ws, void **flags, void **data);
+int gpuk_ws_set_peer_pointers(gpuk_ws *ws, void *const *flags, void *const *data, int n);
+/* Replaces enable_p2p (src/common/communicator.h:40-55): peer access among devices 0..n-1. */
+int gpuk_enable_peer_access(int n_devices);
+
+/* ------------------------------------------------------------------------------------- */
+/* graph-capture registration surface (kept for drop-in compatibility)                   */
+/* ------------------------------------------------------------------------------------- */
+
+/*
+ * The reference registers input tensors seen during CUDA-graph capture so that peers can
+ * read them in place (all_reduce_fusion.cpp:105-137, 168-233).  This implementation pushes
+ * data and never reads a peer's input, so a captured call needs no registration: the
+ * captured list is always empty and these calls succeed without effect.  They replace
+ * ar_fusion_capture_clear (:295-298), get_ar_fusion_captured_handles / _offsets (:310-318)
+ * and open_ar_fusion_captured_handles (:320-323).
+ */
+int gpuk_ws_capture_clear(gpuk_ws *ws);
+int gpuk_ws_captured_count(gpuk_ws *ws, int *count);
+int gpuk_ws_open_captured_handles(gpuk_ws *ws, const uint8_t *handles, const int64_t *offsets, int n,
+                                  int64_t ptr_idx);
+/*
+ * Replace get_ar_fusion_tensor_handle / get_ar_fusion_tensor_offset (:300-308): the IPC
+ * handle of the allocation that contains `ptr`, and ptr's byte offset inside it
+ * (ipc_details::create_base_ptr, :36-40).
+ */
+int gpuk_tensor_ipc_handle(const void *ptr, uint8_t out[GPUK_IPC_HANDLE_BYTES]);
+int gpuk_tensor_ipc_offset(const void *ptr, int64_t *offset);
+
+/* ------------------------------------------------------------------------------------- */
+/* the hot path                                                                          */
+/* ------------------------------------------------------------------------------------- */
+
+/*
+ * Replaces allreduce_rms (src/register.cpp:35-40, all_reduce_fusion.cpp:363-396) and
+ * allreduce_rms_fusion_impl (src/impl/all_reduce_fusion_impl.h:424-469).
+ *
+ *   allreduce_in [numel]            this rank's partial, contiguous, rows of `hidden`
+ *   residual_in  [numel]            same on all ranks
+ *   rms_gamma    [hidden]
+ *   residual_out [numel]            = T(allreduce + residual)
+ *   norm_out     [numel]            T, or FP8 bytes when quant_type != 0
+ *   scale_out                       quant 1..3: [numel/hidden] fp32 written; quant 4: [1] fp32 read
+ *
+ * Any hidden that is a multiple of 16 bytes / element size up to 32768 elements (16-bit
+ * types) is accepted (the reference: 1024, 2048, 4096 only, impl.h:389-401).  All device
+ * pointers must be 16-byte aligned.  Asynchronous on `stream` (a cudaStream_t).
+ */
+int gpuk_allreduce_rms(gpuk_ws *ws, const void *allreduce_in, const void *residual_in,
+                       const void *rms_gamma, void *residual_out, void *norm_out, float *scale_out,
+                       int64_t numel, int hidden, int dtype, float eps, int quant_type, void *stream);
+
+/*
+ * Replaces allreduce_inplace (src/register.cpp:33-34, all_reduce_fusion.cpp:340-361) and
+ * allreduce_inplace_impl (impl.h:115-144): sum over ranks, fp32 accumulation in rank order,
+ * one rounding, written back over `data`.  numel * element size must be a multiple of 16.
+ */
+int gpuk_allreduce_inplace(gpuk_ws *ws, void *data, int64_t numel, int dtype, void *stream);
+
+/*
+ * One GPU, no communication: residual add + RMSNorm + FP8 with `in` taking the place of
+ * the all-reduced sum.  The reference has no such entry (GPUKDistEnv leaves fptr = None for
+ * world_size 1, gpuk/__init__.py:72-73, and its fused call then fails); this is what the
+ * Python wrapper dispatches to for a group of one.  Same argument meaning as
+ * gpuk_allreduce_rms.
+ */
+int gpuk_residual_rms_quant(const void *in, const void *residual_in, const void *rms_gamma,
+                            void *residual_out, void *norm_out, float *scale_out, int64_t numel,
+                            int hidden, int dtype, float eps, int quant_type, void *stream);
+
+/* ------------------------------------------------------------------------------------- */
+/* policy, status, self-check                                                            */
+/* ------------------------------------------------------------------------------------- */
+
+/* How a call would be executed; pure host arithmetic, usable without a GPU. */
+typedef struct gpuk_plan {
+    int one_shot;       /* 1: one-shot exchange, 0: two-shot */
+    int vpt;            /* 16-byte vectors of a row held per thread */
+    int threads;        /* CTA size */
+    int rows_per_chunk; /* rows between two flag exchanges (two-shot) */
+    int grid;           /* CTAs per rank */
+    int rows;
+    int row_vecs;
+    int64_t message_bytes;
+} gpuk_plan;
+
+/*
+ * Launch plan for a message of `numel` elements in rows of `hidden` on `world_size` ranks.
+ * ctas_per_sm_limit is the occupancy the caller assumes (<= 0: the built-in default),
+ * oneshot_max_bytes the one-shot/two-shot crossover (<= 0: the built-in default per world
+ * size; the reference's rule is impl.h:375-376).
+ */
+int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype, int sm_count,
+                            int ctas_per_sm_limit, int64_t oneshot_max_bytes, gpuk_plan *out);
+
+/* Override the crossover (bytes of one rank's input; <= 0 restores the default). */
+int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes);
+/* Budget of every device-side wait for a peer, in nanoseconds (default 2 s). */
+int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns);
+
+/*
+ * Copies the workspace's device status words to `out` (synchronises the device):
+ * out[0] = 0 ok / 1 wait timed out / 2 poll cap reached, out[1] = rank, out[2] = CTA,
+ * out[3] = stage, out[4] = peer waited for, out[5] = expected flag, out[6] = flag seen.
+ * Returns GPUK_ERR_PEER_TIMEOUT if out[0] != 0.  The reference spins forever instead
+ * (communicator.h:98-99).
+ */
+int gpuk_ws_status(gpuk_ws *ws, uint32_t out[8]);
+/* Clears the status words and the abort latch (call on all ranks, device idle). */
+int gpuk_ws_clear_status(gpuk_ws *ws);
+
+/*
+ * Self-check of the bounded wait: one CTA waits, with the workspace's time budget, for a
+ * flag that nothing sets, records the timeout and returns.  No fault, no hang; used by the
+ * failure-detection test.
+ */
+int gpuk_ws_selftest_wait(gpuk_ws *ws, void *stream);
+
+/*
+ * The N-rank kernels run for all ranks inside ONE cooperative launch on the current GPU
+ * (block b plays CTA b % grid of rank b / grid), against `world_size` workspaces created
+ * on that GPU and wired together with gpuk_ws_set_peer_pointers.  For validating the
+ * multi-rank logic where a single GPU is available.  Pointer arrays are indexed by rank;
+ * for the plain all-reduce pass residual_in = NULL and hidden = 0 (then `allreduce_in[r]`
+ * is reduced in place).  force_mode: 0 = policy decides, 1 = one-shot, 2 = two-shot.
+ */
+int gpuk_emulated_allreduce_rms(gpuk_ws *const *ws, int world_size, void *const *allreduce_in,
+                                const void *residual_in, const void *rms_gamma, void *const *residual_out,
+                                void *const *norm_out, float *const *scale_out, int64_t numel, int hidden,
+                                int dtype, float eps, int quant_type, int force_mode, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GPUK_B200_H_ */

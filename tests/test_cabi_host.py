@@ -1,0 +1,89 @@
+"""CPU-side checks of the boundary: the C-ABI library loads and exports what the header
+declares, argument validation happens before any CUDA call, and the launch policy is sane."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from gpuk_b200 import cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "gpuk_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gpuk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = _declared()
+    assert len(names) >= 25
+    for n in names:
+        assert hasattr(cabi.lib, n), n
+    assert set(names) == set(cabi._SIGNATURES), set(names) ^ set(cabi._SIGNATURES)
+
+
+def test_header_cites_the_reference_for_each_entry_point():
+    text = open(os.path.join(ROOT, "include", "gpuk_b200.h")).read()
+    for needle in ("src/register.cpp", "all_reduce_fusion.cpp", "communicator.h", "all_reduce_fusion_impl.h"):
+        assert needle in text
+
+
+def test_argument_validation_precedes_cuda():
+    """Same failures as init_ar_fusion (src/ops/all_reduce_fusion.cpp:256-266), as status codes."""
+    h = ctypes.c_void_p()
+    for world in (0, 1, 3, 5, 16):
+        assert cabi.lib.gpuk_ws_create(0, 0, world, 1 << 20, 0, ctypes.byref(h)) == cabi.ERR_INVALID_ARGUMENT
+        assert "world size is not supported" in cabi.last_error()
+    assert cabi.lib.gpuk_ws_create(0, 2, 2, 1 << 20, 0, ctypes.byref(h)) == cabi.ERR_INVALID_ARGUMENT
+    assert "invalid rank" in cabi.last_error()
+    assert cabi.lib.gpuk_ws_create(0, -1, 2, 1 << 20, 0, ctypes.byref(h)) == cabi.ERR_INVALID_ARGUMENT
+    assert cabi.lib.gpuk_ws_create(0, 0, 2, 0, 0, ctypes.byref(h)) == cabi.ERR_INVALID_ARGUMENT
+    assert cabi.lib.gpuk_ws_destroy(None) == cabi.OK
+    assert cabi.lib.gpuk_ws_status(None, None) == cabi.ERR_INVALID_ARGUMENT
+    assert cabi.lib.gpuk_allreduce_inplace(None, None, 16, 0, None) == cabi.ERR_INVALID_ARGUMENT
+    assert cabi.lib.gpuk_status_string(cabi.ERR_PEER_TIMEOUT).decode().startswith("timed out")
+
+
+def test_plan_benchmark_configs():
+    sms = 148
+    c2 = cabi.plan(8, 8 * 8192, 8192, sm_count=sms)
+    assert c2.one_shot == 1 and c2.grid == 8 and c2.rows == 8 and c2.row_vecs == 1024
+    assert c2.vpt * c2.threads >= c2.row_vecs
+    c3 = cabi.plan(8, 1024 * 8192, 8192, sm_count=sms)
+    assert c3.one_shot == 0 and c3.message_bytes == 16 << 20
+    assert c3.grid * c3.rows_per_chunk <= 1024 and c3.grid <= 2048
+    c4 = cabi.plan(8, 16384 * 7168, 7168, sm_count=sms)
+    assert c4.one_shot == 0 and c4.row_vecs == 896 and c4.vpt * c4.threads >= 896 and c4.threads % 32 == 0
+    c5 = cabi.plan(8, 32 * 8192, 8192, sm_count=sms)
+    assert c5.message_bytes == 512 << 10
+    one_gpu = cabi.plan(1, 16384 * 7168, 7168, sm_count=sms)
+    assert one_gpu.one_shot == 0 and one_gpu.grid <= sms * 8
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_plan_crossover_moves_with_the_threshold(world):
+    numel = 64 * 4096
+    lo = cabi.plan(world, numel, 4096, oneshot_max_bytes=1024)
+    hi = cabi.plan(world, numel, 4096, oneshot_max_bytes=1 << 21)
+    assert lo.one_shot == 0 and hi.one_shot == 1
+
+
+def test_plan_rejects_bad_shapes():
+    p = cabi.Plan()
+    f = cabi.lib.gpuk_plan_allreduce_rms
+    assert f(8, 4 * 1020, 1020, cabi.DTYPE_BF16, 148, 0, 0, ctypes.byref(p)) == cabi.ERR_UNSUPPORTED
+    assert f(8, 4 * 1024 + 8, 1024, cabi.DTYPE_BF16, 148, 0, 0, ctypes.byref(p)) == cabi.ERR_INVALID_ARGUMENT
+    assert f(3, 4 * 1024, 1024, cabi.DTYPE_BF16, 148, 0, 0, ctypes.byref(p)) == cabi.ERR_INVALID_ARGUMENT
+    assert f(8, 4 * 1024, 1024, 7, 148, 0, 0, ctypes.byref(p)) == cabi.ERR_UNSUPPORTED
+    assert f(8, 2 * 65536, 65536, cabi.DTYPE_BF16, 148, 0, 0, ctypes.byref(p)) == cabi.ERR_UNSUPPORTED
+    assert f(8, 1027, 0, cabi.DTYPE_BF16, 148, 0, 0, ctypes.byref(p)) == cabi.ERR_UNSUPPORTED
+
+
+def test_plan_tiles_cover_every_legal_row():
+    for hidden in range(8, 32768 + 1, 8 * 37):
+        p = cabi.plan(8, 4 * hidden, hidden)
+        assert p.vpt in (1, 2, 4, 8) and p.threads % 32 == 0 and p.threads <= (512 if p.vpt >= 4 else 1024)
+        assert p.vpt * p.threads >= p.row_vecs == hidden // 8

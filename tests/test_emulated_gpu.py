@@ -1,0 +1,119 @@
+"""The N-rank kernels on ONE GPU: all ranks of a group run inside one cooperative launch
+(gpuk_emulated_allreduce_rms), so the exchange logic, the flag protocol and the fused
+epilogue are checked against the T1 oracle without needing N GPUs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import epilogue_oracle as eo   # noqa: E402
+from oracle import inputs as oin           # noqa: E402
+from tests import util                     # noqa: E402
+
+ONE_SHOT, TWO_SHOT = 1, 2
+
+
+def _check_all_ranks(outs, want, quant):
+    for r, got in enumerate(outs):
+        util.check_against_oracle(got, want, quant)
+        # every rank must hold the same bits (same summation order everywhere)
+        assert torch.equal(got[0].view(torch.uint8), outs[0][0].view(torch.uint8)), r
+        assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8)), r
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("mode", [ONE_SHOT, TWO_SHOT])
+@pytest.mark.parametrize("tokens,hidden,quant", [
+    (1, 4096, 3), (8, 8192, 4), (129, 1024, 1), (128, 1024, 2), (37, 7168, 3), (16, 2048, 0), (5, 2056, 3),
+])
+def test_fused_bf16(world, mode, tokens, hidden, quant):
+    parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 1000 + tokens + hidden)
+    static = 0.05 if quant == 4 else None
+    with util.EmulatedGroup(world) as g:
+        outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=mode)
+    want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
+    _check_all_ranks(outs, want, quant)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("mode", [ONE_SHOT, TWO_SHOT])
+def test_fused_other_dtypes(dtype, mode):
+    """fp32 and fp16 at 129 x 1024, as in test/test_all_reduce_fusion.py:177-204."""
+    for world in (2, 8):
+        parts, res, w = util.random_case(world, 129, 1024, dtype, seed=world + 77)
+        with util.EmulatedGroup(world) as g:
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, 3, force_mode=mode)
+        want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
+        for got in outs:
+            # fp32 has no rounding points to pin the sum, so the residual is compared by tolerance
+            util.check_against_oracle(got, want, 3, exact_residual=dtype != torch.float32)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_two_shot_many_chunks_per_cta(world):
+    """More rows than resident CTAs: every CTA pipelines several chunks (push k+1, reduce k,
+    epilogue k-1), the regime of the prefill benchmark."""
+    parts, res, w = util.random_case(world, 1500, 1024, torch.bfloat16, seed=5 + world)
+    with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, 3, force_mode=TWO_SHOT)
+    want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
+    _check_all_ranks(outs, want, 3)
+
+
+def test_back_to_back_calls_mixed_shapes_and_modes():
+    """One workspace, a sequence of calls that changes shape and exchange mode: exercises the
+    epoch counter, the one-shot double buffer and staging reuse."""
+    world = 4
+    seq = [(8, 2048, ONE_SHOT), (8, 2048, ONE_SHOT), (8, 2048, ONE_SHOT), (300, 1024, TWO_SHOT), (8, 2048, ONE_SHOT),
+           (64, 4096, TWO_SHOT), (64, 4096, TWO_SHOT), (3, 1024, ONE_SHOT), (700, 1024, TWO_SHOT), (1, 8192, ONE_SHOT)]
+    with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        for i, (tokens, hidden, mode) in enumerate(seq):
+            parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=100 + i)
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, 3, force_mode=mode)
+            want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
+            _check_all_ranks(outs, want, 3)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("mode", [ONE_SHOT, TWO_SHOT])
+@pytest.mark.parametrize("numel", [8, 4096, 8 * 1024 + 8, 300 * 1024 + 64])
+def test_plain_allreduce(world, mode, numel):
+    """allreduce_inplace: fp32 accumulation in rank order, one rounding
+    (test/cpp/test_all_reduce.cpp:565-587), including a ragged last row."""
+    g0 = torch.Generator().manual_seed(numel + world)
+    parts = [torch.randn(numel, generator=g0).to(torch.bfloat16) for _ in range(world)]
+    want = eo.allreduce_t1(parts)
+    with util.EmulatedGroup(world) as g:
+        outs = g.plain([p.cuda() for p in parts], force_mode=mode)
+    for got in outs:
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def test_plain_allreduce_f32():
+    g0 = torch.Generator().manual_seed(1)
+    parts = [torch.randn(5000, generator=g0) for _ in range(4)]
+    want = eo.allreduce_t1(parts)
+    with util.EmulatedGroup(4) as g:
+        outs = g.plain([p.cuda() for p in parts], force_mode=TWO_SHOT)
+    for got in outs:
+        torch.testing.assert_close(got, want, atol=1e-6, rtol=1e-6)
+
+
+def test_benchmark_decode_config_eight_ranks():
+    """Config 2 (8 x 8192, partials ~N(0,1)/sqrt(8), static scale 0.05) and config 5's message."""
+    for name in ("c2", "c5"):
+        cfg = oin.CONFIGS[name]
+        parts, res, w = oin.make_case(cfg, 8)
+        with util.EmulatedGroup(8) as g:
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), cfg.eps, cfg.quant_type, cfg.static_scale)
+        want = eo.epilogue_t1(parts, res, w, cfg.eps, cfg.quant_type, cfg.static_scale)
+        _check_all_ranks(outs, want, cfg.quant_type)
+
+
+def test_message_larger_than_workspace_is_an_error():
+    from gpuk_b200 import cabi
+    parts, res, w = util.random_case(2, 64, 4096, torch.bfloat16, seed=1)
+    with util.EmulatedGroup(2, max_bytes=64 * 1024) as g:
+        with pytest.raises(cabi.GpukError) as e:
+            g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, 3)
+        assert e.value.status == cabi.ERR_TOO_LARGE

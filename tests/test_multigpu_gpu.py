@@ -1,0 +1,158 @@
+"""Real multi-GPU runs (skipped when fewer than two GPUs are visible).
+
+* one process owning all GPUs with peer access enabled, like the reference's C++ harness
+  (test/cpp/test_all_reduce.cpp:337-356,652-653);
+* one process per GPU with NCCL bootstrap and CUDA-IPC handle exchange through GPUKDistEnv,
+  like test/test_all_reduce_fusion.py:30-98, compared with the oracle (T1) and with the live
+  NCCL path (T2).
+"""
+import ctypes
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import epilogue_oracle as eo   # noqa: E402
+from tests import util                     # noqa: E402
+
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+needs2 = pytest.mark.skipif(NGPU < 2, reason="needs at least two GPUs")
+
+
+def _worlds():
+    return [w for w in (2, 4, 8) if w <= NGPU] or [2]
+
+
+class PeerGroup:
+    """One workspace per device, wired by raw peer pointers inside one process."""
+
+    def __init__(self, world, max_bytes=64 << 20):
+        from gpuk_b200 import cabi
+        self.cabi = cabi
+        self.world = world
+        cabi.check(cabi.lib.gpuk_enable_peer_access(world))
+        self.ws = []
+        for r in range(world):
+            h = ctypes.c_void_p()
+            cabi.check(cabi.lib.gpuk_ws_create(r, r, world, max_bytes, 0, ctypes.byref(h)))
+            self.ws.append(h)
+        flags = (ctypes.c_void_p * world)()
+        data = (ctypes.c_void_p * world)()
+        for r in range(world):
+            f, d = ctypes.c_void_p(), ctypes.c_void_p()
+            cabi.check(cabi.lib.gpuk_ws_local_pointers(self.ws[r], ctypes.byref(f), ctypes.byref(d)))
+            flags[r], data[r] = f, d
+        for r in range(world):
+            cabi.check(cabi.lib.gpuk_ws_set_peer_pointers(self.ws[r], flags, data, world))
+
+    def close(self):
+        for h in self.ws:
+            self.cabi.lib.gpuk_ws_destroy(h)
+
+    def fused(self, parts, residual, weight, eps, quant, static_scale=None):
+        cabi = self.cabi
+        dev = [(parts[r].cuda(r), residual.cuda(r), weight.cuda(r)) for r in range(self.world)]
+        outs = [util.alloc_outputs(dev[r][0], quant, static_scale) for r in range(self.world)]
+        hidden = parts[0].shape[-1]
+        for r in range(self.world):      # launches are asynchronous: all ranks are in flight together
+            with torch.cuda.device(r):
+                x, res, w = dev[r]
+                cabi.check(cabi.lib.gpuk_allreduce_rms(
+                    self.ws[r], util.ptr(x), util.ptr(res), util.ptr(w), util.ptr(outs[r][0]), util.ptr(outs[r][1]),
+                    util.ptr(outs[r][2]), x.numel(), hidden, cabi.dtype_code(x.dtype), eps, quant,
+                    ctypes.c_void_p(torch.cuda.current_stream(r).cuda_stream)))
+        for r in range(self.world):
+            torch.cuda.synchronize(r)
+        for r in range(self.world):
+            out = (ctypes.c_uint32 * 8)()
+            assert cabi.lib.gpuk_ws_status(self.ws[r], out) == 0, list(out)
+        return [(o[0].cpu(), o[1].cpu(), o[2].cpu() if quant else None) for o in outs]
+
+
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_single_process_peer_access(world):
+    g = PeerGroup(world)
+    try:
+        for i, (tokens, hidden, quant) in enumerate([(8, 8192, 4), (8, 8192, 3), (129, 1024, 1), (1024, 8192, 3),
+                                                     (8, 8192, 3), (37, 7168, 2), (2048, 7168, 3), (1, 4096, 0)]):
+            parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 100 + i)
+            static = 0.05 if quant == 4 else None
+            outs = g.fused(parts, res, w, 1e-6, quant, static)
+            want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
+            for got in outs:
+                util.check_against_oracle(got, want, quant)
+                assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8))
+    finally:
+        g.close()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _ipc_worker(rank, world, port, cases, q):
+    import torch.distributed as dist
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    import gpuk_b200
+    from gpuk_b200 import cabi
+    env = gpuk_b200.GPUKDistEnv(group=None, device_id=rank, max_size_in_bytes=64 << 20)
+    failures = []
+    try:
+        for i, (tokens, hidden, fp8_out) in enumerate(cases):
+            parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=900 + i)
+            x = parts[rank].cuda()
+            r_d, w_d = res.cuda(), w.cuda()
+            got = env.allreduce_add_rms_fused(x.clone(), r_d, w_d, 1e-6, fp8_out)
+            nat = env.allreduce_add_rms_native(x.clone(), r_d, w_d, 1e-6, fp8_out)
+            torch.cuda.synchronize()
+            quant = 3 if fp8_out else 0
+            want = eo.epilogue_t1(parts, res, w, 1e-6, quant)
+            got_c = (got[0].cpu(), got[1].cpu(), got[2].cpu() if fp8_out else None)
+            try:
+                util.check_against_oracle(got_c, want, quant)
+                if world == 2:   # a two-rank bf16 collective is a single add: the live path must agree too
+                    nat_c = (nat[0].cpu(), nat[1].cpu(), nat[2].cpu() if fp8_out else None)
+                    util.check_against_oracle(got_c, nat_c, quant)
+                plain = env.allreduce(x)
+                assert torch.equal(plain.cpu().view(torch.int16), eo.allreduce_t1(parts).view(torch.int16))
+            except AssertionError as e:   # pragma: no cover
+                failures.append(f"case {i} {tokens}x{hidden}: {e}")
+        out = (ctypes.c_uint32 * 8)()
+        rc = cabi.lib.gpuk_ws_status(ctypes.c_void_p(env.fptr), out)
+        if rc:
+            failures.append(f"status {list(out)}")
+    finally:
+        q.put((rank, failures))
+        env.barrier()
+        del env
+        dist.destroy_process_group()
+
+
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_one_process_per_gpu_over_ipc(world):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    cases = [(8, 8192, True), (1, 4096, True), (129, 1024, True), (1024, 8192, True), (8, 8192, False), (512, 7168, True)]
+    port = _free_port()
+    procs = [ctx.Process(target=_ipc_worker, args=(r, world, port, cases, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+    for rank, failures in results:
+        assert not failures, (rank, failures)
+    assert all(p.exitcode == 0 for p in procs)
