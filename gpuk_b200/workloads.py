@@ -1,4 +1,4 @@
-"""Seeded synthetic inputs for the benchmark configurations (test infrastructure).
+"""Seeded synthetic inputs for the benchmark configurations.
 
 All tensors are drawn on the CPU from a seeded ``torch.Generator`` and cast to the
 working dtype, so the CPU oracle and the GPU kernels see identical bits.  There is no

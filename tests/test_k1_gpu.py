@@ -8,7 +8,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from oracle import epilogue_oracle as eo          # noqa: E402
-from oracle import inputs as oin                  # noqa: E402
+from gpuk_b200 import workloads as oin                  # noqa: E402
 from tests import util                            # noqa: E402
 from tests.test_oracle import GOLDEN, load_golden  # noqa: E402
 
