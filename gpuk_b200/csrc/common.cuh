@@ -83,8 +83,35 @@ struct Elem<__nv_bfloat16> {
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
-    // value of x after one round-to-nearest-even to the storage type
-    __device__ static __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+    // elementwise T(a * b): the product of two bf16 values is exact in fp32, so one packed
+    // multiply rounds exactly like "convert, multiply in fp32, round"
+    __device__ static __forceinline__ uint4 mul(const uint4 &a, const uint4 &b) {
+        const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&wa[i]),
+                                       *reinterpret_cast<const __nv_bfloat162 *>(&wb[i]));
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // running maximum of magnitudes, kept as a packed pair
+    using AbsMax = uint32_t;
+    __device__ static __forceinline__ AbsMax absmax_init() { return 0u; }
+    __device__ static __forceinline__ void absmax_update(AbsMax &m, const uint4 &a) {
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t mag = w[i] & 0x7fff7fffu;
+            __nv_bfloat162 h = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&m),
+                                       *reinterpret_cast<const __nv_bfloat162 *>(&mag));
+            m = *reinterpret_cast<uint32_t *>(&h);
+        }
+    }
+    __device__ static __forceinline__ float absmax_value(AbsMax m) {
+        return fmaxf(__uint_as_float(m << 16), __uint_as_float(m & 0xffff0000u));
+    }
 };
 
 template <>
@@ -108,7 +135,31 @@ struct Elem<__half> {
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
-    __device__ static __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+    __device__ static __forceinline__ uint4 mul(const uint4 &a, const uint4 &b) {
+        const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __hmul2(*reinterpret_cast<const __half2 *>(&wa[i]), *reinterpret_cast<const __half2 *>(&wb[i]));
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    using AbsMax = uint32_t;
+    __device__ static __forceinline__ AbsMax absmax_init() { return 0u; }
+    __device__ static __forceinline__ void absmax_update(AbsMax &m, const uint4 &a) {
+        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t mag = w[i] & 0x7fff7fffu;
+            __half2 h = __hmax2(*reinterpret_cast<const __half2 *>(&m), *reinterpret_cast<const __half2 *>(&mag));
+            m = *reinterpret_cast<uint32_t *>(&h);
+        }
+    }
+    __device__ static __forceinline__ float absmax_value(AbsMax m) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&m));
+        return fmaxf(v.x, v.y);
+    }
 };
 
 template <>
@@ -123,7 +174,19 @@ struct Elem<float> {
     __device__ static __forceinline__ uint4 pack(const float (&f)[4]) {
         return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
     }
-    __device__ static __forceinline__ float round(float x) { return x; }
+    __device__ static __forceinline__ uint4 mul(const uint4 &a, const uint4 &b) {
+        return make_uint4(__float_as_uint(__uint_as_float(a.x) * __uint_as_float(b.x)),
+                          __float_as_uint(__uint_as_float(a.y) * __uint_as_float(b.y)),
+                          __float_as_uint(__uint_as_float(a.z) * __uint_as_float(b.z)),
+                          __float_as_uint(__uint_as_float(a.w) * __uint_as_float(b.w)));
+    }
+    using AbsMax = float;
+    __device__ static __forceinline__ AbsMax absmax_init() { return 0.f; }
+    __device__ static __forceinline__ void absmax_update(AbsMax &m, const uint4 &a) {
+        m = fmaxf(fmaxf(m, fabsf(__uint_as_float(a.x))), fabsf(__uint_as_float(a.y)));
+        m = fmaxf(fmaxf(m, fabsf(__uint_as_float(a.z))), fabsf(__uint_as_float(a.w)));
+    }
+    __device__ static __forceinline__ float absmax_value(AbsMax m) { return m; }
 };
 
 // ---------------------------------------------------------------------------------------

@@ -91,7 +91,7 @@ bool quant_from_type(int quant_type, Quant *q) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int max_threads_for(int vpt) { return vpt >= 4 ? 512 : 1024; }
+int max_threads_for(int vpt) { return vpt == 4 ? 256 : (vpt == 8 ? 512 : 1024); }   // kernels.cuh: tile_max_threads
 
 // Tile of a row: `vpt` 16-byte vectors per thread, `threads` per CTA.
 bool pick_tile(int row_vecs, bool latency, int *vpt, int *threads) {

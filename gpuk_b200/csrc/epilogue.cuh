@@ -13,7 +13,12 @@
 // this epilogue reproduces the PyTorch path instead.
 //
 // One CTA owns a row.  Thread t holds vectors t, t+B, t+2B, ... (B = blockDim.x) of the row
-// so that every warp-wide access is one contiguous 512-byte segment.
+// so that every warp-wide access is one contiguous 512-byte segment.  The row stays packed in
+// registers between the passes; the arithmetic is kept to ~14 instructions per element so
+// that the kernels stay memory-bound: packed multiplies where the packed result rounds
+// identically, and the division by the row's scale done as reciprocal + one exact-residual
+// correction (q = n*y; q += fma(-q, scale, n) * y with y = 1/scale), which returns the
+// correctly rounded quotient.
 #pragma once
 
 #include "common.cuh"
@@ -38,6 +43,9 @@ struct EpilogueSmem {
     float red[2][2][32];
 };
 
+// The RMSNorm weight is re-read for every row (it stays in L1/L2) instead of being held in
+// registers across rows: that keeps the register footprint low enough for four 256-thread
+// CTAs per SM.  Loads are issued before the first block reduction so their latency is hidden.
 template <typename T, int VPT>
 __device__ __forceinline__ void load_gamma(const EpilogueArgs &a, uint4 (&g)[VPT]) {
 #pragma unroll
@@ -47,11 +55,23 @@ __device__ __forceinline__ void load_gamma(const EpilogueArgs &a, uint4 (&g)[VPT
     }
 }
 
-// `x[i]` holds the all-reduced sum (already rounded to T) for vector threadIdx.x + i*blockDim.x
-// of row `row`; on return the row's residual_out / norm_out / scale_out have been written.
+// Issues the loads of this thread's residual vectors of `row` (all in flight together).
+template <typename T, int VPT>
+__device__ __forceinline__ void load_residual(const EpilogueArgs &a, int64_t row, uint4 (&res)[VPT]) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(a.residual) + row * a.row_vecs;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        res[i] = v < a.row_vecs ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
+    }
+}
+
+// `x[i]` holds the all-reduced sum (already rounded to T) and `res[i]` the residual for vector
+// threadIdx.x + i*blockDim.x of row `row` (zeros beyond the row); on return the row's
+// residual_out / norm_out / scale_out have been written.
 template <typename T, int VPT>
 __device__ __forceinline__ void row_epilogue(const EpilogueArgs &a, int64_t row, uint4 (&x)[VPT],
-                                             const uint4 (&g)[VPT], EpilogueSmem &sm, int parity,
+                                             const uint4 (&res)[VPT], EpilogueSmem &sm, int parity,
                                              float static_scale) {
     constexpr int KV = Elem<T>::kVec;
     const int64_t row_base = row * a.row_vecs;
@@ -60,64 +80,65 @@ __device__ __forceinline__ void row_epilogue(const EpilogueArgs &a, int64_t row,
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * blockDim.x;
-        if (v < a.row_vecs) {
-            float s[KV], r[KV];
-            Elem<T>::unpack(x[i], s);
-            Elem<T>::unpack(ld_stream(reinterpret_cast<const uint4 *>(a.residual) + row_base + v), r);
+        float s[KV], r[KV];
+        Elem<T>::unpack(x[i], s);
+        Elem<T>::unpack(res[i], r);
 #pragma unroll
-            for (int e = 0; e < KV; ++e) {
-                r[e] = Elem<T>::round(s[e] + r[e]);
-                ss += r[e] * r[e];
-            }
-            x[i] = Elem<T>::pack(r);
-            st_stream(reinterpret_cast<uint4 *>(a.residual_out) + row_base + v, x[i]);
-        }
+        for (int e = 0; e < KV; ++e) r[e] += s[e];
+        x[i] = Elem<T>::pack(r);
+        if (v < a.row_vecs) st_stream(reinterpret_cast<uint4 *>(a.residual_out) + row_base + v, x[i]);
+        Elem<T>::unpack(x[i], r);
+#pragma unroll
+        for (int e = 0; e < KV; ++e) ss = fmaf(r[e], r[e], ss);
     }
+    uint4 g[VPT];
+    load_gamma<T, VPT>(a, g);
     ss = block_sum(ss, sm.red[parity][0]);
-    const float rstd = rsqrtf(ss / static_cast<float>(a.hidden) + a.eps);
+    const float rstd = 1.0f / sqrtf(ss / static_cast<float>(a.hidden) + a.eps);
 
-    float amax = 0.f;
+    typename Elem<T>::AbsMax am = Elem<T>::absmax_init();
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * blockDim.x;
-        if (v < a.row_vecs) {
-            float r[KV], w[KV];
-            Elem<T>::unpack(x[i], r);
-            Elem<T>::unpack(g[i], w);
+        float r[KV];
+        Elem<T>::unpack(x[i], r);
 #pragma unroll
-            for (int e = 0; e < KV; ++e) {
-                r[e] = Elem<T>::round(w[e] * Elem<T>::round(r[e] * rstd));
-                amax = fmaxf(amax, fabsf(r[e]));
-            }
-            x[i] = Elem<T>::pack(r);
-            if (a.q.mode == kQuantNone) st_stream(reinterpret_cast<uint4 *>(a.norm_out) + row_base + v, x[i]);
-        }
+        for (int e = 0; e < KV; ++e) r[e] *= rstd;
+        x[i] = Elem<T>::mul(g[i], Elem<T>::pack(r));
+        Elem<T>::absmax_update(am, x[i]);
+        if (a.q.mode == kQuantNone && v < a.row_vecs)
+            st_stream(reinterpret_cast<uint4 *>(a.norm_out) + row_base + v, x[i]);
     }
     if (a.q.mode == kQuantNone) return;
 
     float scale = static_scale;
     if (a.q.mode == kQuantDynamic) {
-        amax = block_max(amax, sm.red[parity][1]);
+        const float amax = block_max(Elem<T>::absmax_value(am), sm.red[parity][1]);
         scale = amax == 0.f ? 1.f : amax / a.q.fp8_max;
         if (threadIdx.x == 0) a.scale_out[row] = scale;
     }
-    const float lim = a.q.fp8_max;
+    // |n / scale| <= fp8_max by construction for the dynamic policies and the static policy
+    // saturates at the format maximum, so the saturating convert is the clamp.
+    const float y = 1.0f / scale;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * blockDim.x;
-        if (v < a.row_vecs) {
-            float n[KV];
-            Elem<T>::unpack(x[i], n);
+        float n[KV], q[KV];
+        Elem<T>::unpack(x[i], n);
 #pragma unroll
-            for (int e = 0; e < KV; ++e) n[e] = fminf(fmaxf(n[e] / scale, -lim), lim);
+        for (int e = 0; e < KV; ++e) {
+            q[e] = n[e] * y;
+            q[e] = copysignf(fmaf(fmaf(-q[e], scale, n[e]), y, q[e]), n[e]);   // keeps the sign of a zero
+        }
+        if (v < a.row_vecs) {
             uint8_t *dst = reinterpret_cast<uint8_t *>(a.norm_out) + (row_base + v) * KV;
             if constexpr (KV == 8) {
                 uint2 o;
-                o.x = cvt_e4m3x4(n[0], n[1], n[2], n[3], a.q.fnuz);
-                o.y = cvt_e4m3x4(n[4], n[5], n[6], n[7], a.q.fnuz);
+                o.x = cvt_e4m3x4(q[0], q[1], q[2], q[3], a.q.fnuz);
+                o.y = cvt_e4m3x4(q[4], q[5], q[6], q[7], a.q.fnuz);
                 __stcs(reinterpret_cast<uint2 *>(dst), o);
             } else {
-                __stcs(reinterpret_cast<uint32_t *>(dst), cvt_e4m3x4(n[0], n[1], n[2], n[3], a.q.fnuz));
+                __stcs(reinterpret_cast<uint32_t *>(dst), cvt_e4m3x4(q[0], q[1], q[2], q[3], a.q.fnuz));
             }
         }
     }

@@ -29,11 +29,20 @@
 //              on every rank works on the same rows, so all synchronisation is between CTAs
 //              of equal index (the structural idea of communicator.h:82-88), and a CTA
 //              software-pipelines its chunks: push k+1, reduce k, epilogue k-1.
+//
+// Every loop that moves data issues a batch of independent 16-byte loads before the first
+// dependent store, because a store to memory that may alias the source stops the compiler
+// from hoisting later loads above it.
 #pragma once
 
 #include "epilogue.cuh"
 
 namespace gpuk {
+
+template <int VPT>
+constexpr int tile_max_threads() { return VPT == 4 ? 256 : (VPT == 8 ? 512 : 1024); }
+template <int VPT>
+constexpr int tile_min_blocks() { return VPT == 4 ? 4 : 1; }
 
 // ---------------------------------------------------------------------------------------
 // one GPU: residual add + RMSNorm + FP8, no communication
@@ -45,21 +54,21 @@ struct NormQuantParams {
 };
 
 template <typename T, int VPT>
-__global__ void __launch_bounds__(VPT >= 4 ? 512 : 1024)
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>())
     fused_norm_quant_kernel(const __grid_constant__ NormQuantParams p) {
     __shared__ EpilogueSmem sm;
-    uint4 g[VPT], x[VPT];
-    load_gamma<T, VPT>(p.ep, g);
     const float static_scale = p.ep.q.mode == kQuantStatic ? *p.ep.scale_out : 1.f;
     int parity = 0;
     for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
         const uint4 *src = reinterpret_cast<const uint4 *>(p.in) + row * p.ep.row_vecs;
+        uint4 x[VPT], res[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * blockDim.x;
             x[i] = v < p.ep.row_vecs ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
         }
-        row_epilogue<T, VPT>(p.ep, row, x, g, sm, parity, static_scale);
+        load_residual<T, VPT>(p.ep, row, res);
+        row_epilogue<T, VPT>(p.ep, row, x, res, sm, parity, static_scale);
     }
 }
 
@@ -108,21 +117,49 @@ __device__ __forceinline__ int row_len(const ArParams &p, int row) {
     return left < p.row_vecs ? static_cast<int>(left) : p.row_vecs;
 }
 
+template <typename T, int NR>
+__device__ __forceinline__ uint4 sum_in_rank_order(const uint4 (&part)[NR]) {
+    constexpr int KV = Elem<T>::kVec;
+    float acc[KV];
+    Elem<T>::unpack(part[0], acc);
+#pragma unroll
+    for (int s = 1; s < NR; ++s) {
+        float f[KV];
+        Elem<T>::unpack(part[s], f);
+#pragma unroll
+        for (int e = 0; e < KV; ++e) acc[e] += f[e];
+    }
+    return Elem<T>::pack(acc);
+}
+
 // ---- two-shot stages -------------------------------------------------------------------
 
 // Stage 1: scatter the slices of rows [r0, r1) of my partial to their owners.
 template <typename T, int NR>
 __device__ __forceinline__ void push_slices(const ArParams &p, int r0, int r1) {
+    constexpr int U = 4;
     const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
+    const int B = blockDim.x;
     for (int row = r0; row < r1; ++row) {
         const int len = row_len(p, row);
         const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
-        for (int v = threadIdx.x; v < len; v += blockDim.x) {
-            const int owner = v / p.vpr;
-            if (owner == p.rank) continue;   // my own slice is summed straight from `in`
-            const uint4 val = ld_stream(in + base + v);
-            char *slot = p.peer_data[owner] + p.rank * p.rs_slot_bytes;
-            st_peer(reinterpret_cast<uint4 *>(slot) + static_cast<int64_t>(row) * p.vpr + (v - owner * p.vpr), val);
+        for (int v0 = threadIdx.x; v0 < len; v0 += U * B) {
+            uint4 val[U];
+            int owner[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int v = v0 + u * B;
+                owner[u] = v < len ? v / p.vpr : p.rank;     // my own slice is summed straight from `in`
+                if (owner[u] != p.rank) val[u] = ld_stream(in + base + v);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int v = v0 + u * B;
+                if (owner[u] != p.rank) {
+                    char *slot = p.peer_data[owner[u]] + p.rank * p.rs_slot_bytes;
+                    st_peer(reinterpret_cast<uint4 *>(slot) + static_cast<int64_t>(row) * p.vpr + (v - owner[u] * p.vpr), val[u]);
+                }
+            }
         }
     }
 }
@@ -131,64 +168,80 @@ __device__ __forceinline__ void push_slices(const ArParams &p, int r0, int r1) {
 // write the result into every rank's gather area.
 template <typename T, int NR>
 __device__ __forceinline__ void reduce_and_gather(const ArParams &p, int r0, int r1) {
-    constexpr int KV = Elem<T>::kVec;
+    constexpr int IB = NR >= 8 ? 1 : (NR == 4 ? 2 : 4);   // items per batch: ~8 loads in flight per thread
     const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
     const int items = (r1 - r0) * p.vpr;
-    for (int it = threadIdx.x; it < items; it += blockDim.x) {
-        const int rr = it / p.vpr;
-        const int vl = it - rr * p.vpr;
-        const int row = r0 + rr;
-        const int v = p.rank * p.vpr + vl;
-        if (v >= row_len(p, row)) continue;
-        uint4 part[NR];
+    const int B = blockDim.x;
+    for (int it0 = threadIdx.x; it0 < items; it0 += IB * B) {
+        uint4 part[IB][NR];
+        int64_t dst[IB];
 #pragma unroll
-        for (int s = 0; s < NR; ++s) {
-            if (s == p.rank) {
-                part[s] = ld_stream(in + static_cast<int64_t>(row) * p.row_vecs + v);
-            } else {
-                const char *slot = p.peer_data[p.rank] + s * p.rs_slot_bytes;
-                part[s] = ld_staging(reinterpret_cast<const uint4 *>(slot) + static_cast<int64_t>(row) * p.vpr + vl);
+        for (int b = 0; b < IB; ++b) {
+            const int it = it0 + b * B;
+            dst[b] = -1;
+            if (it < items) {
+                const int rr = it / p.vpr;
+                const int vl = it - rr * p.vpr;
+                const int row = r0 + rr;
+                const int v = p.rank * p.vpr + vl;
+                if (v < row_len(p, row)) {
+                    dst[b] = static_cast<int64_t>(row) * p.row_vecs + v;
+#pragma unroll
+                    for (int s = 0; s < NR; ++s) {
+                        if (s == p.rank) {
+                            part[b][s] = ld_stream(in + dst[b]);
+                        } else {
+                            const char *slot = p.peer_data[p.rank] + s * p.rs_slot_bytes;
+                            part[b][s] = ld_staging(reinterpret_cast<const uint4 *>(slot) + static_cast<int64_t>(row) * p.vpr + vl);
+                        }
+                    }
+                }
             }
         }
-        float acc[KV];
-        Elem<T>::unpack(part[0], acc);
 #pragma unroll
-        for (int s = 1; s < NR; ++s) {
-            float f[KV];
-            Elem<T>::unpack(part[s], f);
+        for (int b = 0; b < IB; ++b) {
+            if (dst[b] >= 0) {
+                const uint4 red = sum_in_rank_order<T, NR>(part[b]);
 #pragma unroll
-            for (int e = 0; e < KV; ++e) acc[e] += f[e];
-        }
-        const uint4 red = Elem<T>::pack(acc);
-        const int64_t dst = static_cast<int64_t>(row) * p.row_vecs + v;
-#pragma unroll
-        for (int d = 0; d < NR; ++d) {
-            const int j = (p.rank + d) % NR;   // start with myself, then fan out: spreads the links
-            st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + p.ag_off) + dst, red);
+                for (int d = 0; d < NR; ++d) {
+                    const int j = (p.rank + d) % NR;   // start with myself, then fan out: spreads the links
+                    st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + p.ag_off) + dst[b], red);
+                }
+            }
         }
     }
 }
 
 // Stage 3: rows [r0, r1) are complete in my gather area.
 template <typename T, int NR, int VPT, bool FUSED>
-__device__ __forceinline__ void finish_rows(const ArParams &p, int r0, int r1, const uint4 (&g)[VPT],
-                                            EpilogueSmem &sm, int &parity, float static_scale) {
+__device__ __forceinline__ void finish_rows(const ArParams &p, int r0, int r1, EpilogueSmem &sm, int &parity,
+                                            float static_scale) {
     const uint4 *ag = reinterpret_cast<const uint4 *>(p.peer_data[p.rank] + p.ag_off);
     for (int row = r0; row < r1; ++row) {
         const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
         if constexpr (FUSED) {
-            uint4 x[VPT];
+            uint4 x[VPT], res[VPT];
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = threadIdx.x + i * blockDim.x;
                 x[i] = v < p.row_vecs ? ld_staging(ag + base + v) : make_uint4(0, 0, 0, 0);
             }
-            row_epilogue<T, VPT>(p.ep, row, x, g, sm, parity, static_scale);
+            load_residual<T, VPT>(p.ep, row, res);
+            row_epilogue<T, VPT>(p.ep, row, x, res, sm, parity, static_scale);
             parity ^= 1;
         } else {
+            constexpr int U = 4;
             const int len = row_len(p, row);
-            for (int v = threadIdx.x; v < len; v += blockDim.x)
-                st_stream(reinterpret_cast<uint4 *>(p.out) + base + v, ld_staging(ag + base + v));
+            const int B = blockDim.x;
+            for (int v0 = threadIdx.x; v0 < len; v0 += U * B) {
+                uint4 val[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (v0 + u * B < len) val[u] = ld_staging(ag + base + v0 + u * B);
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (v0 + u * B < len) st_stream(reinterpret_cast<uint4 *>(p.out) + base + v0 + u * B, val[u]);
+            }
         }
     }
 }
@@ -196,13 +249,10 @@ __device__ __forceinline__ void finish_rows(const ArParams &p, int r0, int r1, c
 // ---- the body: one CTA of one rank ------------------------------------------------------
 template <typename T, int NR, int VPT, bool TWO_SHOT, bool FUSED>
 __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, EpilogueSmem &sm) {
-    constexpr int KV = Elem<T>::kVec;
     LocalState *st = p.st;
     const uint32_t base = ld_volatile_u32(&st->epoch);
-    uint4 g[VPT];
     float static_scale = 1.f;
     if constexpr (FUSED) {
-        load_gamma<T, VPT>(p.ep, g);
         if (p.ep.q.mode == kQuantStatic) static_scale = *p.ep.scale_out;
     }
     int parity = 0;
@@ -227,12 +277,12 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
             signal_peers<NR>(p, 1, vb, base + k + 1);
             if (k > 0) {
                 wait_peers<NR>(p, 1, vb, base + k);
-                finish_rows<T, NR, VPT, FUSED>(p, r0_of(k - 1), r1_of(k - 1), g, sm, parity, static_scale);
+                finish_rows<T, NR, VPT, FUSED>(p, r0_of(k - 1), r1_of(k - 1), sm, parity, static_scale);
             }
         }
         if (nk > 0) {
             wait_peers<NR>(p, 1, vb, base + nk);
-            finish_rows<T, NR, VPT, FUSED>(p, r0_of(nk - 1), r1_of(nk - 1), g, sm, parity, static_scale);
+            finish_rows<T, NR, VPT, FUSED>(p, r0_of(nk - 1), r1_of(nk - 1), sm, parity, static_scale);
         }
     } else {
         // one-shot: one row per step, no pipelining (the regime is a handful of rows per CTA)
@@ -243,53 +293,50 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
             const int row = vb + k * nb;   // rows_per_chunk is 1 on this path
             const int len = row_len(p, row);
             const int64_t rbase = static_cast<int64_t>(row) * p.row_vecs;
-            uint4 mine[VPT];
+            uint4 x[VPT], res[VPT];
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = threadIdx.x + i * blockDim.x;
-                mine[i] = make_uint4(0, 0, 0, 0);
+                x[i] = v < len ? ld_stream(in + rbase + v) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int v = threadIdx.x + i * blockDim.x;
                 if (v < len) {
-                    mine[i] = ld_stream(in + rbase + v);
 #pragma unroll
                     for (int d = 1; d < NR; ++d) {
                         const int j = (p.rank + d) % NR;
-                        st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + buf_off + p.rank * p.os_slot_bytes) + rbase + v,
-                                mine[i]);
+                        st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + buf_off + p.rank * p.os_slot_bytes) + rbase + v, x[i]);
                     }
                 }
             }
             signal_peers<NR>(p, 0, vb, base + k + 1);
+            if constexpr (FUSED) load_residual<T, VPT>(p.ep, row, res);   // in flight while the peers' pushes arrive
             wait_peers<NR>(p, 0, vb, base + k + 1);
-            uint4 x[VPT];
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = threadIdx.x + i * blockDim.x;
-                x[i] = make_uint4(0, 0, 0, 0);
                 if (v < len) {
                     uint4 part[NR];
 #pragma unroll
                     for (int s = 0; s < NR; ++s) {
                         part[s] = s == p.rank
-                                      ? mine[i]
+                                      ? x[i]
                                       : ld_staging(reinterpret_cast<const uint4 *>(p.peer_data[p.rank] + buf_off +
                                                                                    s * p.os_slot_bytes) + rbase + v);
                     }
-                    float acc[KV];
-                    Elem<T>::unpack(part[0], acc);
-#pragma unroll
-                    for (int s = 1; s < NR; ++s) {
-                        float f[KV];
-                        Elem<T>::unpack(part[s], f);
-#pragma unroll
-                        for (int e = 0; e < KV; ++e) acc[e] += f[e];
-                    }
-                    x[i] = Elem<T>::pack(acc);
-                    if constexpr (!FUSED) st_stream(reinterpret_cast<uint4 *>(p.out) + rbase + v, x[i]);
+                    x[i] = sum_in_rank_order<T, NR>(part);
                 }
             }
             if constexpr (FUSED) {
-                row_epilogue<T, VPT>(p.ep, row, x, g, sm, parity, static_scale);
+                row_epilogue<T, VPT>(p.ep, row, x, res, sm, parity, static_scale);
                 parity ^= 1;
+            } else {
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int v = threadIdx.x + i * blockDim.x;
+                    if (v < len) st_stream(reinterpret_cast<uint4 *>(p.out) + rbase + v, x[i]);
+                }
             }
         }
     }
@@ -308,11 +355,8 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
     }
 }
 
-template <int VPT>
-constexpr int ar_max_threads() { return VPT >= 4 ? 512 : 1024; }
-
 template <typename T, int NR, int VPT, bool TWO_SHOT, bool FUSED>
-__global__ void __launch_bounds__(ar_max_threads<VPT>())
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>())
     ar_kernel(const __grid_constant__ ArParams p) {
     __shared__ EpilogueSmem sm;
     ar_body<T, NR, VPT, TWO_SHOT, FUSED>(p, blockIdx.x, gridDim.x, sm);
@@ -321,7 +365,7 @@ __global__ void __launch_bounds__(ar_max_threads<VPT>())
 // N ranks in one cooperative launch on one GPU: block b plays CTA (b % nb) of rank (b / nb).
 // All blocks are co-resident (cooperative launch), so the flag waits between "ranks" are safe.
 template <typename T, int NR, int VPT, bool TWO_SHOT, bool FUSED>
-__global__ void __launch_bounds__(ar_max_threads<VPT>())
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>())
     ar_emulated_kernel(const ArParams *params_by_rank, int nb) {
     __shared__ EpilogueSmem sm;
     __shared__ ArParams p;

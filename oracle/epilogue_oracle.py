@@ -165,10 +165,22 @@ class ParityReport:
     fp8_exact_frac: float
     fp8_within_1ulp_frac: float
     scale_max_rel: float
+    scale_rows: int = 0
+    scale_rows_beyond_1e3: int = 0
 
-    def check(self, *, atol=2e-2, rtol=2e-2, fp8_frac=0.999, scale_rel=1e-3) -> None:
+    def check(self, *, fp8_frac=0.999, scale_rel=1e-3, scale_step=2.0 ** -7) -> None:
+        """FP8 codes within one step on >= fp8_frac of the elements; scales within scale_rel.
+
+        The row maximum is a 16-bit value: when the two sides' fp32 row statistics differ in the
+        last bit, that value can round to the neighbouring 16-bit number on one side, which moves
+        the scale by one 16-bit step (2^-8 .. 2^-7 relative).  Such a row is tolerated only as an
+        outlier: at most one row, or 0.1 % of the rows, and never by more than one step.
+        """
         assert self.fp8_within_1ulp_frac >= fp8_frac, self
-        assert self.scale_max_rel <= scale_rel, self
+        assert self.scale_max_rel <= scale_step, self
+        assert self.scale_rows_beyond_1e3 <= max(1, self.scale_rows // 1000), self
+        if self.scale_rows_beyond_1e3 == 0:
+            assert self.scale_max_rel <= scale_rel, self
 
 
 def compare(got, want, *, atol=2e-2, rtol=2e-2) -> ParityReport:
@@ -188,5 +200,7 @@ def compare(got, want, *, atol=2e-2, rtol=2e-2) -> ParityReport:
     near = (d <= 1).sum().item() / n if d.numel() else 1.0
     srel = ((g_scale.float().reshape(-1) - w_scale.float().reshape(-1)).abs()
             / w_scale.float().reshape(-1).abs().clamp_min(1e-30))
+    beyond = int((srel > 1e-3).sum().item()) if srel.numel() else 0
+    rows = srel.numel()
     srel = srel.max().item() if srel.numel() else 0.0
-    return ParityReport(res_mis, res_abs, 0.0, exact, near, srel)
+    return ParityReport(res_mis, res_abs, 0.0, exact, near, srel, rows, beyond)

@@ -127,11 +127,12 @@ def random_case(world, tokens, hidden, dtype, seed):
 
 def check_against_oracle(got, want, quant, *, exact_residual=True, fp8_frac=0.999):
     """The parity bars: bf16 outputs atol/rtol 2e-2, FP8 within one e4m3 step on >= 99.9 % of
-    elements, scales within 1e-3 relative.  The residual stream has no reduction-order
-    freedom, so it is additionally required to be bit-exact."""
+    elements, scales within 1e-3 relative (a row whose 16-bit maximum rounded to the neighbouring
+    value counts as an outlier, see ParityReport.check).  The residual stream has no
+    reduction-order freedom, so it is additionally required to be bit-exact."""
     rep = eo.compare(got, want, atol=2e-2, rtol=2e-2)
     if exact_residual:
         assert rep.residual_mismatch_frac == 0.0, rep
     if quant:
-        rep.check(fp8_frac=fp8_frac, scale_rel=1e-3)
+        rep.check(fp8_frac=fp8_frac, scale_rel=1e-3, scale_step=2.0 ** -7 if got[0].dtype != torch.float16 else 2.0 ** -10)
     return rep
