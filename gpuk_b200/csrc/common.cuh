@@ -96,6 +96,20 @@ struct Elem<__nv_bfloat16> {
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
+    // elementwise T(a + b).  The fp32 sum of two bf16 values is either exact (exponents at most
+    // 16 apart) or dominated by the larger operand, so a packed add with one rounding gives
+    // the same bits as "convert, add in fp32, round".
+    __device__ static __forceinline__ uint4 add(const uint4 &a, const uint4 &b) {
+        const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __hadd2(*reinterpret_cast<const __nv_bfloat162 *>(&wa[i]),
+                                       *reinterpret_cast<const __nv_bfloat162 *>(&wb[i]));
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
     // running maximum of magnitudes, kept as a packed pair
     using AbsMax = uint32_t;
     __device__ static __forceinline__ AbsMax absmax_init() { return 0u; }
@@ -145,6 +159,17 @@ struct Elem<__half> {
         }
         return make_uint4(w[0], w[1], w[2], w[3]);
     }
+    // same argument as for bf16: exact in fp32 up to 13 binades apart, dominated beyond
+    __device__ static __forceinline__ uint4 add(const uint4 &a, const uint4 &b) {
+        const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __half2 h = __hadd2(*reinterpret_cast<const __half2 *>(&wa[i]), *reinterpret_cast<const __half2 *>(&wb[i]));
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
     using AbsMax = uint32_t;
     __device__ static __forceinline__ AbsMax absmax_init() { return 0u; }
     __device__ static __forceinline__ void absmax_update(AbsMax &m, const uint4 &a) {
@@ -180,6 +205,12 @@ struct Elem<float> {
                           __float_as_uint(__uint_as_float(a.z) * __uint_as_float(b.z)),
                           __float_as_uint(__uint_as_float(a.w) * __uint_as_float(b.w)));
     }
+    __device__ static __forceinline__ uint4 add(const uint4 &a, const uint4 &b) {
+        return make_uint4(__float_as_uint(__uint_as_float(a.x) + __uint_as_float(b.x)),
+                          __float_as_uint(__uint_as_float(a.y) + __uint_as_float(b.y)),
+                          __float_as_uint(__uint_as_float(a.z) + __uint_as_float(b.z)),
+                          __float_as_uint(__uint_as_float(a.w) + __uint_as_float(b.w)));
+    }
     using AbsMax = float;
     __device__ static __forceinline__ AbsMax absmax_init() { return 0.f; }
     __device__ static __forceinline__ void absmax_update(AbsMax &m, const uint4 &a) {
@@ -204,23 +235,35 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+// After the barrier every thread reads all per-warp partials with broadcast 16-byte loads and
+// combines them in warp order (same order in every thread, so the result is uniform).
 __device__ __forceinline__ float block_sum(float v, float *sm) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
     v = warp_sum(v);
     if (nwarps == 1) return v;
     if (lane == 0) sm[warp] = v;
+    if (warp == 0 && lane >= nwarps) sm[lane] = 0.f;   // pad to a multiple of four
     __syncthreads();
-    v = lane < nwarps ? sm[lane] : 0.f;
-    return warp_sum(v);
+    float acc = 0.f;
+    for (int i = 0; i < nwarps; i += 4) {
+        const float4 q = *reinterpret_cast<const float4 *>(sm + i);
+        acc += (q.x + q.y) + (q.z + q.w);
+    }
+    return acc;
 }
 __device__ __forceinline__ float block_max(float v, float *sm) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
     v = warp_max(v);
     if (nwarps == 1) return v;
     if (lane == 0) sm[warp] = v;
+    if (warp == 0 && lane >= nwarps) sm[lane] = 0.f;   // operands are magnitudes, so 0 is the identity
     __syncthreads();
-    v = lane < nwarps ? sm[lane] : 0.f;     // operands are magnitudes, so 0 is the identity
-    return warp_max(v);
+    float acc = 0.f;
+    for (int i = 0; i < nwarps; i += 4) {
+        const float4 q = *reinterpret_cast<const float4 *>(sm + i);
+        acc = fmaxf(fmaxf(acc, fmaxf(q.x, q.y)), fmaxf(q.z, q.w));
+    }
+    return acc;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -18,6 +18,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <new>
@@ -95,7 +96,10 @@ int max_threads_for(int vpt) { return vpt == 4 ? 256 : (vpt == 8 ? 512 : 1024); 
 
 // Tile of a row: `vpt` 16-byte vectors per thread, `threads` per CTA.
 bool pick_tile(int row_vecs, bool latency, int *vpt, int *threads) {
-    const int target = latency ? 1024 : 256;
+    int target = latency ? 1024 : 256;
+    // tuning knob for experiments: preferred CTA size of the bandwidth tile
+    static const int forced = [] { const char *e = getenv("GPUK_TILE_THREADS"); return e ? atoi(e) : 0; }();
+    if (!latency && forced >= 32 && forced <= 1024) target = forced;
     int v = 1;
     while (v < 8 && row_vecs > v * target) v *= 2;
     while ((row_vecs + v - 1) / v > max_threads_for(v)) {

@@ -39,7 +39,7 @@ struct EpilogueArgs {
 
 // Shared memory for the two block reductions of a row, double-buffered by row parity so
 // that consecutive rows need no extra barrier between them.
-struct EpilogueSmem {
+struct alignas(16) EpilogueSmem {
     float red[2][2][32];
 };
 
@@ -80,12 +80,8 @@ __device__ __forceinline__ void row_epilogue(const EpilogueArgs &a, int64_t row,
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * blockDim.x;
-        float s[KV], r[KV];
-        Elem<T>::unpack(x[i], s);
-        Elem<T>::unpack(res[i], r);
-#pragma unroll
-        for (int e = 0; e < KV; ++e) r[e] += s[e];
-        x[i] = Elem<T>::pack(r);
+        float r[KV];
+        x[i] = Elem<T>::add(x[i], res[i]);
         if (v < a.row_vecs) st_stream(reinterpret_cast<uint4 *>(a.residual_out) + row_base + v, x[i]);
         Elem<T>::unpack(x[i], r);
 #pragma unroll
