@@ -348,6 +348,7 @@ def main():
 
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
+    os.environ.setdefault("NCCL_DEBUG", "WARN")      # keeps NCCL's version banner off stdout
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     else:

@@ -22,7 +22,7 @@ package_name = "gpuk"   # operator namespace, as in the reference (gpuk/__init__
 filename = os.path.join(this_dir, "libgpuk_b200.so")
 if not os.path.exists(filename):
     raise ImportError(
-        f"{filename} is missing: build it with `python -m gpuk_b200._build` (needs nvcc and g++; "
+        f"{filename} is missing: build it with `python gpuk_b200/_build.py` (needs nvcc and g++; "
         "there is no CPU fallback)")
 
 from . import cabi  # noqa: E402  (loads libgpuk_core.so first; libgpuk_b200.so links against it)

@@ -1,6 +1,6 @@
 """In-tree build of the native libraries (sm_100a only).
 
-    python -m gpuk_b200._build [core] [torch] [oracle]
+    python gpuk_b200/_build.py [core] [torch] [oracle]
 
 * ``libgpuk_core.so``  the CUDA kernels and the C ABI of ``include/gpuk_b200.h`` (nvcc, no torch)
 * ``libgpuk_b200.so``  the PyTorch operator library ``torch.ops.gpuk.*`` on top of it (g++)

@@ -32,7 +32,7 @@ class GpukError(RuntimeError):
 
 if not os.path.exists(CORE_LIB):
     raise ImportError(
-        f"{CORE_LIB} is missing: build it with `python -m gpuk_b200._build` (needs nvcc; there is no CPU fallback)")
+        f"{CORE_LIB} is missing: build it with `python gpuk_b200/_build.py` (needs nvcc; there is no CPU fallback)")
 
 lib = ctypes.CDLL(CORE_LIB)
 
@@ -59,6 +59,7 @@ _SIGNATURES = {
     "gpuk_residual_rms_quant": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_float, c_int, _P]),
     "gpuk_plan_allreduce_rms": (c_int, [c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, POINTER(Plan)]),
     "gpuk_ws_set_oneshot_max_bytes": (c_int, [_P, c_int64]),
+    "gpuk_ws_set_option": (c_int, [_P, c_char_p, c_int64]),
     "gpuk_ws_set_timeout_ns": (c_int, [_P, c_uint64]),
     "gpuk_ws_status": (c_int, [_P, POINTER(c_uint32)]),
     "gpuk_ws_clear_status": (c_int, [_P]),

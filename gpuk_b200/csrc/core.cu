@@ -57,6 +57,7 @@ constexpr int kDefaultSmCount = 148;            // B200
 constexpr int64_t kOneShotSlotBytes = 2 << 20;  // largest one-shot message
 constexpr int64_t kRsSlack = 1 << 20;           // room for ceil(row_vecs / N) rounding in the RS slots
 constexpr uint64_t kDefaultTimeoutNs = 2000000000ull;
+constexpr int kDefaultRoles = 1;                // two-shot CTA organisation unless GPUK_ROLES says otherwise
 constexpr int kPlainRowVecs = 1024;             // the plain all-reduce views its input as 16 KiB rows
 
 int elem_size(int dtype) {
@@ -129,6 +130,7 @@ struct gpuk_ws {
     bool have_data = false, have_flags = false;
     std::vector<void *> ipc_opened;
     int64_t oneshot_max_bytes = 0;
+    int opt_roles = 0, opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default / environment
     std::map<uint32_t, int> occupancy;   // resident CTAs per SM, by kernel instantiation
 };
 
@@ -188,12 +190,17 @@ int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype
         if (!fused) { vpt = 4; threads = std::max(32, ((row_vecs + 3) / 4 + 31) / 32 * 32); }
     }
     int per_sm = std::max(1, std::min(4, 1024 / threads));
+    // tuning knobs for experiments (read once): CTAs per SM and rows per flag exchange
+    static const int env_per_sm = [] { const char *e = getenv("GPUK_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+    static const int env_rpc = [] { const char *e = getenv("GPUK_ROWS_PER_CHUNK"); return e ? atoi(e) : 0; }();
+    if (env_per_sm > 0) per_sm = std::min(per_sm, env_per_sm);
     if (ctas_per_sm_limit > 0) per_sm = std::min(per_sm, ctas_per_sm_limit);
     const int64_t cta_cap = std::min<int64_t>(static_cast<int64_t>(sm_count) * per_sm, kMaxBlocks);
     int rpc = 1;
     if (world_size > 1 && !one_shot) {
         const int vpr = (row_vecs + world_size - 1) / world_size;
         if (rows > cta_cap) rpc = std::max(1, std::min(4, (threads + vpr - 1) / vpr));
+        if (env_rpc > 0) rpc = std::min(env_rpc, 64);
     }
     const int64_t nchunks = (rows + rpc - 1) / rpc;
     int64_t grid;
@@ -422,6 +429,25 @@ int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes) {
     ws->oneshot_max_bytes = bytes > 0 ? bytes : 0;
     return GPUK_OK;
 }
+int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
+    if (!ws || !name) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace or option name");
+    const std::string n(name);
+    if (n == "roles") {
+        if (value != 0 && value != 1 && value != 3) return fail(GPUK_ERR_INVALID_ARGUMENT, "roles must be 0, 1 or 3");
+        ws->opt_roles = static_cast<int>(value);
+    } else if (n == "rows_per_chunk") {
+        if (value < 0 || value > 64) return fail(GPUK_ERR_INVALID_ARGUMENT, "rows_per_chunk must be in [0, 64]");
+        ws->opt_rows_per_chunk = static_cast<int>(value);
+    } else if (n == "ctas_per_sm") {
+        if (value < 0 || value > 16) return fail(GPUK_ERR_INVALID_ARGUMENT, "ctas_per_sm must be in [0, 16]");
+        ws->opt_ctas_per_sm = static_cast<int>(value);
+    } else if (n == "oneshot_max_bytes") {
+        return gpuk_ws_set_oneshot_max_bytes(ws, value);
+    } else {
+        return fail(GPUK_ERR_INVALID_ARGUMENT, "unknown option '%s'", name);
+    }
+    return GPUK_OK;
+}
 int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns) {
     if (!ws || ns == 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace or zero budget");
     GPUK_CUDA(cudaSetDevice(ws->device));
@@ -541,6 +567,8 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         if (rc) return rc;
         if ((plan.one_shot != 0) != one_shot) return fail(GPUK_ERR_UNSUPPORTED, "requested exchange mode is not available for this shape");
     }
+    if (!one_shot && ws->opt_rows_per_chunk > 0) plan.rows_per_chunk = std::min(ws->opt_rows_per_chunk, 64);
+    if (ws->opt_ctas_per_sm > 0) plan.grid = std::min<int64_t>(plan.grid, static_cast<int64_t>(ws->sm_count) * ws->opt_ctas_per_sm);
     const int es = elem_size(a.dtype);
     memset(p, 0, sizeof(*p));
     p->in = a.in;
@@ -592,6 +620,18 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     int64_t resident = static_cast<int64_t>(per_sm) * ws->sm_count;
     if (emulated) resident /= ws->world;
     const int64_t nchunks = (static_cast<int64_t>(plan.rows) + plan.rows_per_chunk - 1) / plan.rows_per_chunk;
+    static const int env_roles_ = [] { const char *e = getenv("GPUK_ROLES"); return e ? atoi(e) : 0; }();
+    const int env_roles = ws->opt_roles ? ws->opt_roles : env_roles_;
+    const int roles = (!one_shot && (env_roles == 3 || (env_roles == 0 && kDefaultRoles == 3)) && resident >= 3) ? 3 : 1;
+    p->roles = roles;
+    if (roles == 3) {
+        // lanes of three specialised CTAs; flag rows are indexed by lane
+        int64_t lanes = std::min<int64_t>(std::min<int64_t>(resident, kMaxBlocks) / 3, nchunks);
+        if (lanes < 1) lanes = 1;
+        shape->grid = static_cast<int>(lanes * 3);
+        p->epoch_advance = static_cast<uint32_t>((nchunks + lanes - 1) / lanes + 1);
+        return GPUK_OK;
+    }
     int64_t grid = std::min<int64_t>(std::min<int64_t>(plan.grid, resident), nchunks);
     if (grid < 1) grid = 1;
     shape->grid = static_cast<int>(grid);

@@ -95,19 +95,23 @@ struct ArParams {
     int64_t os_off;          // one-shot: offset of buffer 0
     int64_t os_slot_bytes;   // one-shot: stride between slots; a buffer is N slots
     uint32_t epoch_advance;  // how far this call moves the flag epoch
+    int roles;               // two-shot: 1 = every CTA runs all three stages of its chunks,
+                             // 3 = CTAs specialise (3*lane + {0: push, 1: reduce+gather, 2: epilogue})
 };
 
+// `with_self`: also raise / await this rank's own flag.  Needed when the data of a stage is
+// produced and consumed by different CTAs of the same rank (specialised roles).
 template <int NR>
-__device__ __forceinline__ void signal_peers(const ArParams &p, int stage, int vb, uint32_t value) {
+__device__ __forceinline__ void signal_peers(const ArParams &p, int stage, int vb, uint32_t value, bool with_self = false) {
     __syncthreads();   // every thread's pushes precede the release below (cumulativity)
     const int t = threadIdx.x;
-    if (t < NR && t != p.rank) st_release_sys(p.peer_flags[t] + flag_index(stage, vb, p.rank), value);
+    if (t < NR && (with_self || t != p.rank)) st_release_sys(p.peer_flags[t] + flag_index(stage, vb, p.rank), value);
 }
 
 template <int NR>
-__device__ __forceinline__ void wait_peers(const ArParams &p, int stage, int vb, uint32_t value) {
+__device__ __forceinline__ void wait_peers(const ArParams &p, int stage, int vb, uint32_t value, bool with_self = false) {
     const int t = threadIdx.x;
-    if (t < NR && t != p.rank)
+    if (t < NR && (with_self || t != p.rank))
         wait_flag(p.peer_flags[p.rank] + flag_index(stage, vb, t), value, p.st, p.rank, vb, stage, t);
     __syncthreads();   // the acquire above now orders every thread's reads of the pushed data
 }
@@ -260,7 +264,29 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
     const int nchunks = (p.rows + R - 1) / R;
     const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;   // chunks of this CTA: vb, vb+nb, ...
 
-    if constexpr (TWO_SHOT) {
+    if (TWO_SHOT && p.roles == 3) {
+        // Specialised roles: the three stages of a lane's chunks run in three CTAs that only meet
+        // through flags, so pushes stream without ever waiting, reductions start as soon as a
+        // chunk has landed, and the epilogue trails behind -- the stages of different chunks
+        // overlap in time even when a lane owns only a few chunks.
+        const int lanes = nb / 3, lane = vb / 3, role = vb - lane * 3;
+        const int nl = lane < nchunks ? (nchunks - lane + lanes - 1) / lanes : 0;
+        for (int k = 0; k < nl; ++k) {
+            const int r0 = (lane + k * lanes) * R;
+            const int r1 = r0 + R < p.rows ? r0 + R : p.rows;
+            if (role == 0) {
+                push_slices<T, NR>(p, r0, r1);
+                signal_peers<NR>(p, 0, lane, base + k + 1);
+            } else if (role == 1) {
+                wait_peers<NR>(p, 0, lane, base + k + 1);
+                reduce_and_gather<T, NR>(p, r0, r1);
+                signal_peers<NR>(p, 1, lane, base + k + 1, true);
+            } else {
+                wait_peers<NR>(p, 1, lane, base + k + 1, true);
+                finish_rows<T, NR, VPT, FUSED>(p, r0, r1, sm, parity, static_scale);
+            }
+        }
+    } else if constexpr (TWO_SHOT) {
         auto r0_of = [&](int k) { return (vb + k * nb) * R; };
         auto r1_of = [&](int k) { const int r1 = (vb + k * nb) * R + R; return r1 < p.rows ? r1 : p.rows; };
         if (nk > 0) {

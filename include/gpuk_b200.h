@@ -197,6 +197,14 @@ int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype
 
 /* Override the crossover (bytes of one rank's input; <= 0 restores the default). */
 int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes);
+/*
+ * Tuning options of the two-shot exchange; all ranks must set the same values.  Names:
+ * "roles" (1: every CTA runs all stages of its chunks, 3: CTAs specialise into push / reduce /
+ * epilogue, 0: default), "rows_per_chunk" (rows between two flag exchanges, 0: default),
+ * "ctas_per_sm" (cap on resident CTAs per SM, 0: default), "oneshot_max_bytes".
+ * The reference fixes these at compile time (communicator.h:57-58, impl.h:375-376).
+ */
+int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value);
 /* Budget of every device-side wait for a peer, in nanoseconds (default 2 s). */
 int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns);
 

@@ -72,6 +72,10 @@ class EmulatedGroup:
             cabi.lib.gpuk_ws_destroy(h)
         self.ws = []
 
+    def set_option(self, name: str, value: int):
+        for h in self.ws:
+            cabi.check(cabi.lib.gpuk_ws_set_option(h, name.encode(), value))
+
     def __enter__(self):
         return self
 
