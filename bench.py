@@ -172,7 +172,7 @@ def max_over_ranks(seconds, world):
     return float(t.item())
 
 
-def run_config(cfg, env, gpuk, rank, world, steps, warmup, barrier, graph=False):
+def run_config(cfg, env, gpuk, rank, world, steps, warmup, barrier, graph=False, native=False):
     device = torch.device("cuda", torch.cuda.current_device())
     nsets = sets_needed(cfg)
     sets, w = make_sets(cfg, rank, world, nsets, device)
@@ -202,6 +202,25 @@ def run_config(cfg, env, gpuk, rank, world, steps, warmup, barrier, graph=False)
         reps = max(1, steps // per_graph)
         secs_g = max_over_ranks(time_calls(lambda i: g.replay(), 1, reps, max(3, warmup // per_graph), barrier), world)
         out["us_per_call_graph"] = secs_g / (reps * per_graph) * 1e6
+    if world > 1 and native:
+        # comparison on the same GPUs: NCCL all-reduce + the unfused PyTorch operator sequence
+        x0, r0 = sets[0][0], sets[0][1]
+        xn = x0.clone()
+
+        def call_native(i):
+            xn.copy_(x0)
+            if cfg.quant_type == 4:
+                import torch.distributed as dist
+                dist.all_reduce(xn)
+                ro = xn + r0
+                v = ro.float().pow(2).mean(-1, keepdim=True)
+                n = w * (ro * torch.rsqrt(v + cfg.eps)).to(ro.dtype)
+                (n.float() / cfg.static_scale).clamp_(-448, 448).to(torch.float8_e4m3fn)
+            else:
+                env.allreduce_add_rms_native(xn, r0, w, cfg.eps, True)
+
+        k = max(5, min(steps, 50))
+        out["us_per_call_nccl_unfused"] = max_over_ranks(time_calls(call_native, 1, k, 3, barrier), world) / k * 1e6
     us = out.get("us_per_call_graph", out["us_per_call"]) if graph else out["us_per_call"]
     if world == 1:
         gbs = hbm_bytes(cfg.tokens, cfg.hidden) / (out["us_per_call"] * 1e-6) / 1e9
@@ -369,7 +388,7 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    head = run_config(cfg, env, gpuk, rank, world, args.steps, args.warmup, barrier)
+    head = run_config(cfg, env, gpuk, rank, world, args.steps, args.warmup, barrier, native=True)
     # keep the same kernel running a little longer so the 100 ms clock sampler sees it under load
     extra = max(0, int(0.4 / max(head["us_per_call"] * 1e-6, 1e-7)) - args.steps)
     if extra:
@@ -386,7 +405,7 @@ def main():
             c = oin.CONFIGS[key]
             k = max(10, min(args.steps, 20000 if c.tokens <= 64 else (300 if c.tokens >= 8192 else 2000)))
             sweep.append(run_config(c, env, gpuk, rank, world, k, min(args.warmup, 20), barrier,
-                                    graph=c.tokens <= 64))
+                                    graph=c.tokens <= 64, native=True))
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -418,6 +437,7 @@ def main():
                        "quant": "per-token dynamic e4m3fn /448", "l2": f"rotating {head['buffer_sets']} buffer sets (> 4x L2)"},
             "busbw_gbs": roof["achieved"] if world > 1 else None,
             "roofline": roof, "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
+            "nccl_unfused_us_per_call": head.get("us_per_call_nccl_unfused"),
             "cpu_baseline": cpu, "sweep": sweep,
         }
         print(json.dumps(line), flush=True)
