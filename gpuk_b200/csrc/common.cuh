@@ -1,6 +1,6 @@
 // Device-side building blocks shared by every kernel of the tensor-parallel epilogue:
 // 16-byte vector access, element traits with explicit rounding, warp/block reductions,
-// the hardware FP8 cast, and the cross-GPU flag primitives with bounded waits.
+// the hardware FP8 cast, and the cross-GPU hand-off primitives with bounded waits.
 //
 // Replaces, for sm_100a only, the reference's src/common/kernel_utils.h:29-99 (vec_t,
 // warp_reduce, block_reduce), src/common/communicator.h:12-36,79-113 (st_flag, ld_flag,
@@ -15,8 +15,7 @@
 namespace gpuk {
 
 constexpr int kMaxRanks = 8;        // communicator.h:57
-constexpr int kMaxBlocks = 2048;    // CTA indices that own a flag row (reference: 80, communicator.h:58)
-constexpr int kFlagStages = 2;      // stage 0: "my push has landed", stage 1: "my reduced slice has landed"
+constexpr int kMaxBlocks = 2048;    // upper bound on CTAs per rank (reference: 80, communicator.h:58)
 constexpr int kStatusWords = 8;
 
 // ---------------------------------------------------------------------------------------
@@ -34,13 +33,16 @@ struct Quant {
 // device-resident state of one rank's workspace (local, never mapped by peers)
 // ---------------------------------------------------------------------------------------
 struct LocalState {
-    uint32_t epoch;       // base value for this call's flags; advanced by the last CTA of every call
-    uint32_t os_seq;      // number of one-shot calls so far; its low bit selects the one-shot buffer
+    uint32_t seq;         // exchanges completed so far; its low bit selects the staging buffer of the next one
+    uint32_t reserved;
     uint32_t ticket;      // CTAs that have finished the current call
     uint32_t abort;       // set once a wait has run out, so that later waits give up at once
     unsigned long long timeout_ns;
-    uint32_t status[kStatusWords];   // [0]=code (0 ok), [1]=rank, [2]=block, [3]=stage, [4]=peer, [5]=expected, [6]=seen
+    uint32_t status[kStatusWords];   // [0]=code (0 ok), [1]=rank, [2]=CTA, [3]=stage, [4]=peer, [5]=thread, [6]=word seen
 };
+
+// stage codes in status[3]
+enum Stage : int { kStageOneShot = 0, kStageScatter = 1, kStageGather = 2, kStageSelfTest = 3 };
 
 enum StatusCode : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusSpinCap = 2 };
 
@@ -292,15 +294,44 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
 }
 
 // ---------------------------------------------------------------------------------------
-// cross-GPU flags
+// cross-GPU hand-off without flags or fences: the data announces itself
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void st_release_sys(uint32_t *addr, uint32_t v) {
-    asm volatile("st.global.release.sys.b32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *addr) {
-    uint32_t v;
-    asm volatile("ld.global.acquire.sys.b32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+// Staging memory rests in a known state: every 32-bit word holds kEmptyWord.  A producer
+// (a peer GPU, or another CTA of this GPU) overwrites whole 16-byte vectors with payload that
+// never contains that word; the consumer polls the vector until none of its four words is
+// kEmptyWord (aligned 32-bit stores are indivisible, so no ordering between the words or
+// between vectors is needed), uses it, and writes kEmptyWord back so the location is at rest
+// for its next use.  Nothing is fenced and nothing is signalled: NVLink carries only the
+// payload, and a consumer starts the moment its own 16 bytes have landed.
+//
+// kEmptyWord is two negative zeros in the 16-bit formats.  A payload word equal to it is
+// rewritten before it is sent: to two positive zeros for 16-bit types (the sum of partials is
+// unchanged unless every rank contributes -0) and to the neighbouring denormal for fp32.
+//
+// Replaces the counter barrier of src/common/communicator.h:79-113 (st_flag / ld_flag / sync).
+constexpr uint32_t kEmptyWord = 0x80008000u;
+
+template <typename T>
+__device__ __forceinline__ uint4 payload(uint4 v) {
+    constexpr uint32_t repl = sizeof(T) == 4 ? 0x80008001u : 0u;
+    v.x = v.x == kEmptyWord ? repl : v.x;
+    v.y = v.y == kEmptyWord ? repl : v.y;
+    v.z = v.z == kEmptyWord ? repl : v.z;
+    v.w = v.w == kEmptyWord ? repl : v.w;
     return v;
+}
+__device__ __forceinline__ bool landed(const uint4 &v) {
+    return v.x != kEmptyWord && v.y != kEmptyWord && v.z != kEmptyWord && v.w != kEmptyWord;
+}
+// Read of staging memory that another GPU (or CTA) is writing: always served by L2.
+__device__ __forceinline__ uint4 ld_poll(const void *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_empty(void *p) {
+    *reinterpret_cast<uint4 *>(p) = make_uint4(kEmptyWord, kEmptyWord, kEmptyWord, kEmptyWord);
 }
 __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t *addr) {
     uint32_t v;
@@ -316,46 +347,44 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 constexpr uint32_t kSpinCap = 1u << 24;   // hard bound on polls of one wait, independent of the timer
 
 __device__ __forceinline__ void record_status(LocalState *st, uint32_t code, int rank, int block, int stage,
-                                              int peer, uint32_t expected, uint32_t seen) {
+                                              int peer, uint32_t word) {
     if (atomicCAS(&st->status[0], 0u, code) == 0u) {
         st->status[1] = rank;
         st->status[2] = block;
         st->status[3] = stage;
         st->status[4] = peer;
-        st->status[5] = expected;
-        st->status[6] = seen;
+        st->status[5] = threadIdx.x;
+        st->status[6] = word;
     }
     atomicExch(&st->abort, 1u);
 }
 
-// Poll `addr` (local memory that a peer writes) until it reaches `target` in wrap-safe order.
-// Gives up after the workspace's time budget or kSpinCap polls, records where, and returns
-// false; the caller carries on so that the kernel always terminates.
-__device__ __forceinline__ bool wait_flag(const uint32_t *addr, uint32_t target, LocalState *st, int rank,
-                                          int block, int stage, int peer) {
+// `v` is the first read of the vector at `addr`.  Polls until the vector has landed, within the
+// workspace's time budget (and kSpinCap polls); on expiry records where it gave up, latches
+// `abort` so that later waits return at once, and hands back whatever is there: the kernel
+// always terminates.
+static __device__ __noinline__ uint4 wait_landed_slow(const void *addr, uint4 v, LocalState *st, int rank, int stage, int peer) {
     unsigned long long t0 = 0;
-    uint32_t seen = 0;
     for (uint32_t it = 1; it <= kSpinCap; ++it) {
-        seen = ld_acquire_sys(addr);
-        if (static_cast<int32_t>(seen - target) >= 0) return true;
+        __nanosleep(40);
+        v = ld_poll(addr);
+        if (landed(v)) return v;
         if ((it & 63u) == 0u) {
-            unsigned long long now = global_timer_ns();
+            const unsigned long long now = global_timer_ns();
             if (t0 == 0) {
                 t0 = now;
-                if (ld_volatile_u32(&st->abort)) break;
+                if (ld_volatile_u32(&st->abort)) return v;
             } else if (now - t0 > st->timeout_ns || ld_volatile_u32(&st->abort)) {
-                record_status(st, kStatusWaitTimeout, rank, block, stage, peer, target, seen);
-                return false;
+                record_status(st, kStatusWaitTimeout, rank, blockIdx.x, stage, peer, v.x);
+                return v;
             }
         }
     }
-    record_status(st, kStatusSpinCap, rank, block, stage, peer, target, seen);
-    return false;
+    record_status(st, kStatusSpinCap, rank, blockIdx.x, stage, peer, v.x);
+    return v;
 }
-
-__host__ __device__ __forceinline__ size_t flag_index(int stage, int block, int src_rank) {
-    return (static_cast<size_t>(stage) * kMaxBlocks + block) * kMaxRanks + src_rank;
+__device__ __forceinline__ uint4 wait_landed(const void *addr, uint4 v, LocalState *st, int rank, int stage, int peer) {
+    return landed(v) ? v : wait_landed_slow(addr, v, st, rank, stage, peer);
 }
-constexpr size_t kFlagBytes = sizeof(uint32_t) * kFlagStages * kMaxBlocks * kMaxRanks;
 
 }  // namespace gpuk

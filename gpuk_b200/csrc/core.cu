@@ -2,16 +2,19 @@
 // memory, flag array, device-resident state), CUDA-IPC export/import, the launch policy and
 // the entry points.  Replaces src/ops/all_reduce_fusion.cpp:4-396 of the reference.
 //
-// Workspace memory of one rank (one cudaMalloc, exported as one IPC handle):
+// Workspace memory of one rank (one cudaMalloc, exported as one IPC handle), everything
+// double-buffered by call parity and at rest filled with kEmptyWord (common.cuh):
 //
-//   [0, N*rs_slot)              two-shot reduce-scatter slots: slot s holds, for every row, the
-//                               column slice this rank owns as pushed by rank s
-//   [ag_off, ag_off + cap)      two-shot gather area: the reduced tensor, same layout as the input
-//   [os_off, os_off + 2*N*os)   one-shot slots, double-buffered by call parity: slot s of a
-//                               buffer holds rank s's whole message
+//   two-shot buffer b at b*ts_stride:
+//     [0, N*rs_slot)            scatter slots: slot s holds, for every row, the column slice this
+//                               rank owns as pushed by rank s
+//     [ag_off, ag_off + cap)    gather area: the reduced tensor, same layout as the input
+//   one-shot buffer b at os_off + b*N*os_slot: slot s holds rank s's whole message
+//   the last 256 bytes are never written by any exchange (used by the wait self-test)
 //
-// A second, small allocation holds the flags peers write (one row of N counters per CTA index
-// and stage).  The device-resident LocalState (epoch, ticket, status) is never exported.
+// A second, small allocation is exported through the "barrier handle" calls of the operator
+// API; the exchange needs no flags, its words are reserved.  The device-resident LocalState
+// (call counter, ticket, status) is never exported.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -57,6 +60,8 @@ constexpr int kDefaultSmCount = 148;            // B200
 constexpr int64_t kOneShotSlotBytes = 2 << 20;  // largest one-shot message
 constexpr int64_t kRsSlack = 1 << 20;           // room for ceil(row_vecs / N) rounding in the RS slots
 constexpr uint64_t kDefaultTimeoutNs = 2000000000ull;
+constexpr size_t kFlagBytes = 4096;             // the allocation behind the "barrier handle"
+constexpr int64_t kTailBytes = 256;             // never written by an exchange
 constexpr int kDefaultRoles = 1;                // two-shot CTA organisation unless GPUK_ROLES says otherwise
 constexpr int kPlainRowVecs = 1024;             // the plain all-reduce views its input as 16 KiB rows
 
@@ -116,11 +121,24 @@ bool pick_tile(int row_vecs, bool latency, int *vpt, int *threads) {
 
 }  // namespace
 
+namespace {
+__global__ void fill_empty_kernel(uint4 *p, size_t n) {
+    const uint4 e = make_uint4(kEmptyWord, kEmptyWord, kEmptyWord, kEmptyWord);
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) p[i] = e;
+}
+// Puts staging memory into its rest state (synchronous).
+cudaError_t fill_empty(void *p, int64_t bytes) {
+    fill_empty_kernel<<<1184, 256>>>(static_cast<uint4 *>(p), static_cast<size_t>(bytes / 16));
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? cudaDeviceSynchronize() : e;
+}
+}  // namespace
+
 struct gpuk_ws {
     int device = 0, rank = 0, world = 0;
     int sm_count = kDefaultSmCount;
     int64_t cap = 0;            // largest message in bytes
-    int64_t rs_slot_bytes = 0, ag_off = 0, os_off = 0, os_slot_bytes = 0, data_bytes = 0;
+    int64_t rs_slot_bytes = 0, ag_off = 0, ts_stride = 0, os_off = 0, os_slot_bytes = 0, data_bytes = 0;
     char *data = nullptr;
     uint32_t *flags = nullptr;
     LocalState *st = nullptr;
@@ -241,10 +259,12 @@ int gpuk_ws_create(int device_id, int rank, int world_size, int64_t max_size_in_
     ws->cap = (max_size_in_bytes + align - 1) / align * align;
     ws->rs_slot_bytes = ws->cap / world_size + kRsSlack;
     ws->ag_off = ws->rs_slot_bytes * world_size;
-    ws->os_off = ws->ag_off + ws->cap;
+    ws->ts_stride = ws->ag_off + ws->cap;
+    ws->os_off = 2 * ws->ts_stride;
     ws->os_slot_bytes = std::min<int64_t>(ws->cap, kOneShotSlotBytes);
-    ws->data_bytes = ws->os_off + 2 * world_size * ws->os_slot_bytes;
+    ws->data_bytes = ws->os_off + 2 * world_size * ws->os_slot_bytes + kTailBytes;
     cudaError_t e = cudaMalloc(&ws->data, ws->data_bytes);
+    if (e == cudaSuccess) e = fill_empty(ws->data, ws->data_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&ws->flags, kFlagBytes);
     if (e == cudaSuccess) e = cudaMalloc(&ws->st, sizeof(LocalState));
     if (e == cudaSuccess) e = cudaMemset(ws->flags, 0, kFlagBytes);
@@ -463,8 +483,8 @@ int gpuk_ws_status(gpuk_ws *ws, uint32_t out[8]) {
     GPUK_CUDA(cudaMemcpy(&host, ws->st, sizeof(host), cudaMemcpyDeviceToHost));
     memcpy(out, host.status, sizeof(host.status));
     if (out[0] != 0)
-        return fail(GPUK_ERR_PEER_TIMEOUT, "rank %u CTA %u stage %u gave up waiting for rank %u (expected flag %u, saw %u)",
-                    out[1], out[2], out[3], out[4], out[5], out[6]);
+        return fail(GPUK_ERR_PEER_TIMEOUT, "rank %u CTA %u thread %u gave up waiting for data from rank %u in stage %u (word seen 0x%08x)",
+                    out[1], out[2], out[5], out[4], out[3], out[6]);
     return GPUK_OK;
 }
 int gpuk_ws_clear_status(gpuk_ws *ws) {
@@ -473,6 +493,8 @@ int gpuk_ws_clear_status(gpuk_ws *ws) {
     GPUK_CUDA(cudaDeviceSynchronize());
     GPUK_CUDA(cudaMemset(ws->st->status, 0, sizeof(uint32_t) * kStatusWords));
     GPUK_CUDA(cudaMemset(&ws->st->abort, 0, sizeof(uint32_t)));
+    // an exchange that gave up may have left vectors unconsumed: put the staging back to rest
+    GPUK_CUDA(fill_empty(ws->data, ws->data_bytes));
     return GPUK_OK;
 }
 
@@ -483,8 +505,8 @@ int gpuk_ws_clear_status(gpuk_ws *ws) {
 // ---------------------------------------------------------------------------------------
 namespace {
 
-__global__ void selftest_wait_kernel(LocalState *st, const uint32_t *flag, int rank) {
-    if (threadIdx.x == 0) wait_flag(flag, ld_volatile_u32(flag) + 1u, st, rank, 0, 0, rank);
+__global__ void selftest_wait_kernel(LocalState *st, const uint4 *vec, int rank) {
+    if (threadIdx.x == 0) wait_landed(vec, ld_poll(vec), st, rank, kStageSelfTest, rank);
 }
 
 template <typename F>
@@ -582,11 +604,11 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     p->vpr = (plan.row_vecs + ws->world - 1) / ws->world;
     for (int r = 0; r < ws->world; ++r) {
         p->peer_data[r] = static_cast<char *>(ws->peer_data[r]);
-        p->peer_flags[r] = static_cast<uint32_t *>(ws->peer_flags[r]);
     }
     p->st = ws->st;
     p->rs_slot_bytes = ws->rs_slot_bytes;
     p->ag_off = ws->ag_off;
+    p->ts_stride = ws->ts_stride;
     p->os_off = ws->os_off;
     p->os_slot_bytes = ws->os_slot_bytes;
     if (!one_shot && static_cast<int64_t>(plan.rows) * p->vpr * 16 > ws->rs_slot_bytes)
@@ -629,13 +651,11 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         int64_t lanes = std::min<int64_t>(std::min<int64_t>(resident, kMaxBlocks) / 3, nchunks);
         if (lanes < 1) lanes = 1;
         shape->grid = static_cast<int>(lanes * 3);
-        p->epoch_advance = static_cast<uint32_t>((nchunks + lanes - 1) / lanes + 1);
         return GPUK_OK;
     }
     int64_t grid = std::min<int64_t>(std::min<int64_t>(plan.grid, resident), nchunks);
     if (grid < 1) grid = 1;
     shape->grid = static_cast<int>(grid);
-    p->epoch_advance = static_cast<uint32_t>((nchunks + grid - 1) / grid + 1);
     return GPUK_OK;
 }
 
@@ -646,9 +666,9 @@ extern "C" {
 int gpuk_ws_selftest_wait(gpuk_ws *ws, void *stream) {
     if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
     GPUK_CUDA(cudaSetDevice(ws->device));
-    // the flag of (stage 1, last CTA index, own rank) is never written by any kernel
-    const uint32_t *flag = ws->flags + flag_index(1, kMaxBlocks - 1, ws->rank);
-    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ws->st, flag, ws->rank);
+    // the tail of the staging allocation is never written by any exchange
+    const uint4 *vec = reinterpret_cast<const uint4 *>(ws->data + ws->data_bytes - kTailBytes);
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ws->st, vec, ws->rank);
     GPUK_CUDA(cudaGetLastError());
     return GPUK_OK;
 }

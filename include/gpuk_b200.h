@@ -80,7 +80,9 @@ int gpuk_ws_destroy(gpuk_ws *ws);
 /*
  * Replace get_ar_fusion_barrier_handle / get_ar_fusion_data_handle (src/register.cpp:10-13,
  * all_reduce_fusion.cpp:275-283): write the 64-byte cudaIpcMemHandle_t of the flag array /
- * of the staging memory to `out`.
+ * of the staging memory to `out`.  The exchange here needs no flags (data announces itself),
+ * so the flag array is a small reserved allocation; its handle is still exported and opened
+ * so that the reference's bootstrap sequence runs unchanged.
  */
 int gpuk_ws_get_barrier_handle(gpuk_ws *ws, uint8_t out[GPUK_IPC_HANDLE_BYTES]);
 int gpuk_ws_get_data_handle(gpuk_ws *ws, uint8_t out[GPUK_IPC_HANDLE_BYTES]);
@@ -211,17 +213,21 @@ int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns);
 /*
  * Copies the workspace's device status words to `out` (synchronises the device):
  * out[0] = 0 ok / 1 wait timed out / 2 poll cap reached, out[1] = rank, out[2] = CTA,
- * out[3] = stage, out[4] = peer waited for, out[5] = expected flag, out[6] = flag seen.
- * Returns GPUK_ERR_PEER_TIMEOUT if out[0] != 0.  The reference spins forever instead
- * (communicator.h:98-99).
+ * out[3] = stage (0 one-shot, 1 scatter, 2 gather, 3 self-test), out[4] = peer whose data was
+ * awaited, out[5] = thread, out[6] = word seen.  Returns GPUK_ERR_PEER_TIMEOUT if out[0] != 0.
+ * The reference spins forever instead (communicator.h:98-99).
  */
 int gpuk_ws_status(gpuk_ws *ws, uint32_t out[8]);
-/* Clears the status words and the abort latch (call on all ranks, device idle). */
+/*
+ * Clears the status words and the abort latch and puts the staging memory back to its rest
+ * state.  After a timeout every rank of the group must call this, with the device idle, before
+ * the workspace is used again.
+ */
 int gpuk_ws_clear_status(gpuk_ws *ws);
 
 /*
- * Self-check of the bounded wait: one CTA waits, with the workspace's time budget, for a
- * flag that nothing sets, records the timeout and returns.  No fault, no hang; used by the
+ * Self-check of the bounded wait: one thread waits, with the workspace's time budget, for
+ * data that nothing sends, records the timeout and returns.  No fault, no hang; used by the
  * failure-detection test.
  */
 int gpuk_ws_selftest_wait(gpuk_ws *ws, void *stream);
