@@ -66,6 +66,8 @@ _SIGNATURES = {
     "gpuk_ws_selftest_wait": (c_int, [_P, _P]),
     "gpuk_emulated_allreduce_rms": (c_int, [POINTER(_P), c_int, POINTER(_P), _P, _P, POINTER(_P), POINTER(_P),
                                             POINTER(_P), c_int64, c_int, c_int, c_float, c_int, c_int, _P]),
+    "gpuk_selfcheck_allreduce_rms": (c_int, [c_int, POINTER(_P), _P, _P, POINTER(_P), POINTER(_P), POINTER(_P),
+                                             c_int64, c_int, c_int, c_float, c_int, c_int, _P]),
 }
 for _name, (_res, _args) in _SIGNATURES.items():
     _fn = getattr(lib, _name)

@@ -48,6 +48,20 @@ int fail(int code, const char *fmt, ...) {
     return code;
 }
 
+}  // namespace
+
+int gpuk::set_last_error(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+namespace {
+
 #define GPUK_CUDA(expr)                                                                            \
     do {                                                                                           \
         cudaError_t err__ = (expr);                                                                \

@@ -30,4 +30,8 @@ cudaError_t launch_ar_emulated(const ArParams *params_by_rank, const ArShape &s,
 template <typename T>
 cudaError_t ar_blocks_per_sm(const ArShape &s, bool emulated, int *blocks_per_sm);
 
+// Records the text gpuk_last_error() returns on this thread and hands `code` back
+// (defined next to gpuk_last_error).
+int set_last_error(int code, const char *fmt, ...);
+
 }  // namespace gpuk

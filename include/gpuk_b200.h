@@ -245,6 +245,24 @@ int gpuk_emulated_allreduce_rms(gpuk_ws *const *ws, int world_size, void *const 
                                 void *const *norm_out, float *const *scale_out, int64_t numel, int hidden,
                                 int dtype, float eps, int quant_type, int force_mode, void *stream);
 
+/*
+ * No counterpart in the reference.  Same job as gpuk_emulated_allreduce_rms (fused op only)
+ * for callers that must not allocate device memory -- a health probe or test harness inside a
+ * process whose own arena already owns the GPU's memory, where a library-side cudaMalloc may
+ * fail or disturb that arena.  It needs no workspaces: the staging memory is a fixed array
+ * built into the library (about 8.5 MiB, held by every GPU that loads the library until the
+ * process exits), which limits a message to 32 KiB per emulated rank (numel * element size);
+ * larger requests return GPUK_ERR_TOO_LARGE.  Rows longer than 2048 16-byte vectors are not
+ * built.  The first call on a device sets the array up (and synchronises): make it before any
+ * stream capture.  All calls on a device share the array, which keeps the protocol's call
+ * counter between calls; calls that overlap on the GPU race, so issue them one after another.
+ * Allocates nothing (no cudaMalloc, cudaFree or allocating library call).
+ */
+int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allreduce_in, const void *residual_in,
+                                 const void *rms_gamma, void *const *residual_out, void *const *norm_out,
+                                 float *const *scale_out, int64_t numel, int hidden, int dtype, float eps,
+                                 int quant_type, int force_mode, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
