@@ -37,9 +37,9 @@ if ROOT not in sys.path:
 L2_BYTES = 126 << 20
 NVLINK_PEER_COPY_GBS = 770.0      # measured peer copy per direction on this pool (nominal 900)
 HBM_FALLBACK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the one-GPU kernel at the headline
-# shape, from the ncu capture summarised in profiles/ (None until captured)
-K1_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the one-GPU kernel per token at hidden 8192, from the
+# ncu capture summarised in profiles/ (189.7 MB per launch of 4096 tokens; traffic grows with the tokens)
+K1_DRAM_TRAFFIC_BYTES_PER_TOKEN_H8192 = 189.7e6 / 4096
 
 
 def measured_hbm_peak():
@@ -419,7 +419,8 @@ def main():
         if world == 1:
             ach = hbm_bytes(cfg.tokens, cfg.hidden) / (us * 1e-6) / 1e9
             roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "traffic": K1_DRAM_TRAFFIC_BYTES, "peak_kind": f"of {peak_kind}",
+                    "traffic": K1_DRAM_TRAFFIC_BYTES_PER_TOKEN_H8192 * cfg.tokens if cfg.hidden == 8192 else None,
+                    "peak_kind": f"of {peak_kind}",
                     "algorithmic_bytes_per_launch": hbm_bytes(cfg.tokens, cfg.hidden),
                     "kernel": "fused_norm_quant_kernel"}
         else:
