@@ -262,6 +262,50 @@ def run_e2e(cfg, env, rank, world, steps, warmup, barrier):
     return {"value": secs / steps * 1e6, "unit": "us/call", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
 
+def run_model(env, rank, world, steps, warmup, barrier):
+    """Config 5: one decode step (batch 32, context 2048) of the 4-layer tensor-parallel decoder with the
+    fused operator after attention and MLP of every layer, against the same model with NCCL all-reduce and
+    unfused PyTorch operators; eager and replayed from a CUDA graph."""
+    from gpuk_b200.tp_model import DecoderArgs, TPDecoder
+    device = torch.device("cuda", torch.cuda.current_device())
+    args = DecoderArgs()
+    batch, ctx = 32, 2048
+    out = {"workload": "c5_decoder_4layer_dim8192_ffn28672_b32_ctx2048", "batch": batch, "context": ctx, "fp8_activations": True}
+    tokens = torch.randint(0, args.vocab_size, (batch, 1), generator=torch.Generator().manual_seed(11)).to(device)
+    pos = torch.tensor([ctx], device=device)
+    for name, fused in (("fused", True), ("nccl_unfused", False)):
+        model = TPDecoder(args, env, device=device, fused=fused, fp8=True, max_batch=batch)
+        model.fill_kv_cache(ctx)
+
+        def step(_):
+            model.forward(tokens, pos, cache_len=ctx + 1)
+
+        secs = max_over_ranks(time_calls(step, 1, steps, warmup, barrier), world)
+        out[f"us_per_step_{name}"] = secs / steps * 1e6
+        try:
+            g = torch.cuda.CUDAGraph()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                step(0)
+                torch.cuda.synchronize()
+                barrier()
+                with torch.cuda.graph(g, stream=s):
+                    step(0)
+            torch.cuda.current_stream().wait_stream(s)
+            secs = max_over_ranks(time_calls(lambda i: g.replay(), 1, steps, warmup, barrier), world)
+            out[f"us_per_step_{name}_graph"] = secs / steps * 1e6
+            del g
+        except Exception as e:   # a capture failure is reported, not fatal
+            out[f"graph_error_{name}"] = repr(e)[:200]
+        del model
+        torch.cuda.empty_cache()
+        barrier()
+    best = min(v for k, v in out.items() if k.startswith("us_per_step_fused"))
+    out["tokens_per_s_fused"] = batch / (best * 1e-6)
+    return out
+
+
 # ---------------------------------------------------------------------------------------
 # the reference's CPU path on the host cores
 # ---------------------------------------------------------------------------------------
@@ -353,6 +397,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-model", action="store_true", help="skip the decoder-model step (config 5) in the sweep")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -388,7 +433,7 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    head = run_config(cfg, env, gpuk, rank, world, args.steps, args.warmup, barrier, native=True)
+    head = run_config(cfg, env, gpuk, rank, world, args.steps, args.warmup, barrier, native=True, graph=cfg.tokens <= 64)
     # keep the same kernel running a little longer so the 100 ms clock sampler sees it under load
     extra = max(0, int(0.4 / max(head["us_per_call"] * 1e-6, 1e-7)) - args.steps)
     if extra:
@@ -406,6 +451,12 @@ def main():
             k = max(10, min(args.steps, 20000 if c.tokens <= 64 else (300 if c.tokens >= 8192 else 2000)))
             sweep.append(run_config(c, env, gpuk, rank, world, k, min(args.warmup, 20), barrier,
                                     graph=c.tokens <= 64, native=True))
+
+        if not args.no_model:
+            try:
+                sweep.append(run_model(env, rank, world, max(10, min(args.steps, 100)), 5, barrier))
+            except Exception as e:
+                sweep.append({"workload": "c5_decoder", "error": repr(e)[:300]})
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -439,6 +490,7 @@ def main():
             "busbw_gbs": roof["achieved"] if world > 1 else None,
             "roofline": roof, "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
             "nccl_unfused_us_per_call": head.get("us_per_call_nccl_unfused"),
+            "us_per_call_graph": head.get("us_per_call_graph"),
             "cpu_baseline": cpu, "sweep": sweep,
         }
         print(json.dumps(line), flush=True)

@@ -21,7 +21,8 @@ IPC_HANDLE_BYTES = 64
 
 class Plan(ctypes.Structure):
     _fields_ = [("one_shot", c_int), ("vpt", c_int), ("threads", c_int), ("rows_per_chunk", c_int),
-                ("grid", c_int), ("rows", c_int), ("row_vecs", c_int), ("message_bytes", c_int64)]
+                ("grid", c_int), ("rows", c_int), ("row_vecs", c_int), ("message_bytes", c_int64),
+                ("cluster", c_int), ("lead_push", c_int), ("lead_reduce", c_int)]
 
 
 class GpukError(RuntimeError):

@@ -33,9 +33,10 @@ struct Quant {
 // device-resident state of one rank's workspace (local, never mapped by peers)
 // ---------------------------------------------------------------------------------------
 struct LocalState {
-    uint32_t seq;         // exchanges completed so far; its low bit selects the staging buffer of the next one
+    uint32_t seq;         // bits 31..16: exchanges completed so far (the low bit of that number selects the
+                          // staging buffer of the next one); bits 15..0: tickets taken by CTAs of the running call
     uint32_t reserved;
-    uint32_t ticket;      // CTAs that have finished the current call
+    uint32_t reserved2;
     uint32_t abort;       // set once a wait has run out, so that later waits give up at once
     unsigned long long timeout_ns;
     uint32_t status[kStatusWords];   // [0]=code (0 ok), [1]=rank, [2]=CTA, [3]=stage, [4]=peer, [5]=thread, [6]=word seen
@@ -265,6 +266,78 @@ __device__ __forceinline__ float block_max(float v, float *sm) {
         const float4 q = *reinterpret_cast<const float4 *>(sm + i);
         acc = fmaxf(fmaxf(acc, fmaxf(q.x, q.y)), fmaxf(q.z, q.w));
     }
+    return acc;
+}
+
+// ---------------------------------------------------------------------------------------
+// bulk copies (the TMA unit without a tensor map): whole rows travel from global to shared
+// memory asynchronously and announce their arrival on an mbarrier, so a CTA keeps loads in
+// flight while it computes.  Source, destination and size must be multiples of 16 bytes.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+// Makes freshly initialised mbarriers visible to the bulk-copy unit (follow with a block barrier).
+__device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_bytes(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *global_src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(smem_dst)), "l"(global_src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+// Waits for the phase of `bar` with the given parity to complete.  The copies it waits for are
+// this CTA's own and always complete; the loop is bounded all the same and returns false when
+// it gives up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t a = smem_addr(bar);
+    for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// ---------------------------------------------------------------------------------------
+// thread-block clusters: a row may be split over the CTAs of a cluster, which then combine
+// their partial reductions through distributed shared memory.  In a launch without a cluster
+// attribute the cluster is the CTA itself (size 1, rank 0).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ int cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return static_cast<int>(r);
+}
+__device__ __forceinline__ int cluster_size() {
+    uint32_t n;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+    return static_cast<int>(n);
+}
+// Barrier over all threads of the cluster; shared-memory writes made before it (local or to
+// another CTA of the cluster) are visible to every thread of the cluster after it.
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Stores `v` at the address `local` names, but in the shared memory of CTA `cta` of this cluster.
+__device__ __forceinline__ void st_cluster_f32(float *local, int cta, float v) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(local));
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(a), "r"(cta));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+// Every CTA of the cluster passes its own value (uniform across its threads); returns, in every
+// thread of every CTA, the combination of all of them taken in CTA order.  `slots` is this
+// CTA's array of 8 floats; it may be reused after the next cluster_barrier but one.
+template <bool MAX>
+__device__ __forceinline__ float cluster_combine(float v, float *slots, int cl_rank, int cl_size) {
+    if (cl_size == 1) return v;
+    if (threadIdx.x < cl_size) st_cluster_f32(slots + cl_rank, threadIdx.x, v);
+    cluster_barrier();
+    float acc = slots[0];
+    for (int i = 1; i < cl_size; ++i) acc = MAX ? fmaxf(acc, slots[i]) : acc + slots[i];
     return acc;
 }
 

@@ -60,6 +60,61 @@ int gpuk::set_last_error(int code, const char *fmt, ...) {
     return code;
 }
 
+cudaError_t gpuk::launch_kernel(const void *fn, int grid, int threads, int cluster, bool all_resident, void **args,
+                                cudaStream_t stream) {
+    if (cluster <= 1) {
+        return all_resident ? cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(threads), args, 0, stream)
+                            : cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, 0, stream);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = cluster;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeCooperative;
+    attrs[1].val.cooperative = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = all_resident ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
+    if (e != cudaSuccess && all_resident && e != cudaErrorCooperativeLaunchTooLarge) {
+        // The cooperative attribute was not accepted together with a cluster.  The callers of
+        // all_resident launches size the grid with resident_ctas() and every wait in the kernels
+        // is bounded, so the launch goes ahead without it.
+        cudaGetLastError();
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelExC(&cfg, fn, args);
+    }
+    return e;
+}
+
+cudaError_t gpuk::resident_ctas(const void *fn, int threads, int cluster, int sm_count, int64_t *ctas) {
+    if (cluster <= 1) {
+        int per_sm = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, 0);
+        *ctas = static_cast<int64_t>(per_sm) * sm_count;
+        return e;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster * sm_count);
+    cfg.blockDim = dim3(threads);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = cluster;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg);
+    *ctas = static_cast<int64_t>(clusters) * cluster;
+    return e;
+}
+
 namespace {
 
 #define GPUK_CUDA(expr)                                                                            \
@@ -78,6 +133,11 @@ constexpr size_t kFlagBytes = 4096;             // the allocation behind the "ba
 constexpr int64_t kTailBytes = 256;             // never written by an exchange
 constexpr int kDefaultRoles = 1;                // two-shot CTA organisation unless GPUK_ROLES says otherwise
 constexpr int kPlainRowVecs = 1024;             // the plain all-reduce views its input as 16 KiB rows
+constexpr int kDefaultK1Stages = 3;             // shared-memory stages of the one-GPU kernel for many rows (0: off)
+constexpr int kK1StagedMinRowsPerSm = 16;       // ... used from this many rows per SM (measured: 0.94 vs 0.89 of HBM peak
+                                                // at 110 rows per SM, no gain at 7 rows per SM)
+constexpr int kDefaultLeadPush = 1;             // two-shot pipeline depths (chunks), see ar_body
+constexpr int kDefaultLeadReduce = 1;
 
 int elem_size(int dtype) {
     switch (dtype) {
@@ -163,7 +223,8 @@ struct gpuk_ws {
     std::vector<void *> ipc_opened;
     int64_t oneshot_max_bytes = 0;
     int opt_roles = 0, opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default / environment
-    std::map<uint32_t, int> occupancy;   // resident CTAs per SM, by kernel instantiation
+    int opt_lead_push = 0, opt_lead_reduce = 0;
+    std::map<uint32_t, int64_t> occupancy;   // CTAs resident on the whole GPU, by kernel instantiation
 };
 
 extern "C" {
@@ -215,9 +276,20 @@ int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype
     if (oneshot_max_bytes <= 0) oneshot_max_bytes = world_size > 1 ? default_oneshot_max_bytes(world_size) : 0;
     const bool one_shot = world_size > 1 && bytes <= std::min(oneshot_max_bytes, kOneShotSlotBytes) && rows <= kMaxBlocks;
     const bool latency = rows <= sm_count;
+    // One-shot with few rows: a row is split over the CTAs of a thread-block cluster so that the
+    // exchange runs on many SMs, as long as a CTA keeps at least 128 vectors.
+    int cluster = 1;
+    if (one_shot && fused) {
+        while (cluster < 8 && (row_vecs + 2 * cluster - 1) / (2 * cluster) >= 128 && rows * 2 * cluster <= 2ll * sm_count) cluster *= 2;
+        static const int env_cluster = [] { const char *e = getenv("GPUK_CLUSTER"); return e ? atoi(e) : 0; }();
+        if (env_cluster == 1 || env_cluster == 2 || env_cluster == 4 || env_cluster == 8) cluster = env_cluster;
+        while (cluster > 1 && (row_vecs + cluster - 1) / cluster < 32) cluster /= 2;
+    }
+    const int seg_vecs = (row_vecs + cluster - 1) / cluster;
     int vpt = 4, threads = 256;
     if (fused || one_shot) {
-        if (!pick_tile(row_vecs, latency, &vpt, &threads))
+        // the row must fit one CTA's tile whichever exchange is chosen, clusters or not
+        if (!pick_tile(row_vecs, latency, &vpt, &threads) || !pick_tile(seg_vecs, latency, &vpt, &threads))
             return fail(GPUK_ERR_UNSUPPORTED, "row of %d vectors is longer than the largest tile", row_vecs);
         if (!fused) { vpt = 4; threads = std::max(32, ((row_vecs + 3) / 4 + 31) / 32 * 32); }
     }
@@ -237,7 +309,12 @@ int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype
     const int64_t nchunks = (rows + rpc - 1) / rpc;
     int64_t grid;
     if (world_size == 1) grid = std::min<int64_t>(rows, static_cast<int64_t>(sm_count) * 8);
-    else grid = std::min<int64_t>(nchunks, cta_cap);
+    else grid = std::min<int64_t>(nchunks, cta_cap / cluster) * cluster;
+    static const int env_lp = [] { const char *e = getenv("GPUK_LEAD_PUSH"); return e ? atoi(e) : 0; }();
+    static const int env_lr = [] { const char *e = getenv("GPUK_LEAD_REDUCE"); return e ? atoi(e) : 0; }();
+    out->cluster = cluster;
+    out->lead_push = env_lp > 0 ? std::min(env_lp, 1 << 20) : kDefaultLeadPush;
+    out->lead_reduce = env_lr > 0 ? std::min(env_lr, 1 << 20) : kDefaultLeadReduce;
     out->one_shot = one_shot ? 1 : 0;
     out->vpt = vpt;
     out->threads = threads;
@@ -475,6 +552,9 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     } else if (n == "ctas_per_sm") {
         if (value < 0 || value > 16) return fail(GPUK_ERR_INVALID_ARGUMENT, "ctas_per_sm must be in [0, 16]");
         ws->opt_ctas_per_sm = static_cast<int>(value);
+    } else if (n == "lead_push" || n == "lead_reduce") {
+        if (value < 0 || value > (1 << 20)) return fail(GPUK_ERR_INVALID_ARGUMENT, "%s must be in [0, 2^20]", name);
+        (n == "lead_push" ? ws->opt_lead_push : ws->opt_lead_reduce) = static_cast<int>(value);
     } else if (n == "oneshot_max_bytes") {
         return gpuk_ws_set_oneshot_max_bytes(ws, value);
     } else {
@@ -613,6 +693,9 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     p->rows = plan.rows;
     p->row_vecs = plan.row_vecs;
     p->rows_per_chunk = plan.rows_per_chunk;
+    p->seg_vecs = (plan.row_vecs + plan.cluster - 1) / plan.cluster;
+    p->lead_push = std::max(1, ws->opt_lead_push > 0 ? ws->opt_lead_push : plan.lead_push);
+    p->lead_reduce = std::max(1, ws->opt_lead_reduce > 0 ? ws->opt_lead_reduce : plan.lead_reduce);
     if (fused) fill_epilogue(a, q, plan.row_vecs, &p->ep);
     p->rank = ws->rank;
     p->vpr = (plan.row_vecs + ws->world - 1) / ws->world;
@@ -633,28 +716,30 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     shape->two_shot = !one_shot;
     shape->fused = fused;
     shape->threads = plan.threads;
+    shape->cluster = plan.cluster;
+    shape->grid = plan.grid;
     // the grid must be co-resident: CTAs of equal index on different ranks wait for each other
     const uint32_t key = static_cast<uint32_t>(a.dtype) | (plan.vpt << 4) | (one_shot ? 1u << 8 : 0u) |
-                         (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (static_cast<uint32_t>(plan.threads) << 12);
-    int per_sm = 0;
+                         (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (static_cast<uint32_t>(plan.threads) << 12) |
+                         (static_cast<uint32_t>(plan.cluster) << 24);
+    int64_t resident = 0;
     auto cached = ws->occupancy.find(key);
     if (cached != ws->occupancy.end()) {
-        per_sm = cached->second;
+        resident = cached->second;
     } else {
         rc = by_dtype(a.dtype, [&](auto *t) {
             using T = std::remove_pointer_t<decltype(t)>;
-            cudaError_t e = ar_blocks_per_sm<T>(*shape, emulated, &per_sm);
-            if (e != cudaSuccess || per_sm <= 0) {
+            cudaError_t e = ar_resident_ctas<T>(*shape, emulated, ws->sm_count, &resident);
+            if (e != cudaSuccess || resident <= 0) {
                 cudaGetLastError();
                 return fail(GPUK_ERR_CUDA, "occupancy query failed for the selected kernel: %s", cudaGetErrorString(e));
             }
             return static_cast<int>(GPUK_OK);
         });
         if (rc) return rc;
-        ws->occupancy[key] = per_sm;
+        ws->occupancy[key] = resident;
     }
-    int64_t resident = static_cast<int64_t>(per_sm) * ws->sm_count;
-    if (emulated) resident /= ws->world;
+    if (emulated) resident = resident / ws->world / plan.cluster * plan.cluster;
     const int64_t nchunks = (static_cast<int64_t>(plan.rows) + plan.rows_per_chunk - 1) / plan.rows_per_chunk;
     static const int env_roles_ = [] { const char *e = getenv("GPUK_ROLES"); return e ? atoi(e) : 0; }();
     const int env_roles = ws->opt_roles ? ws->opt_roles : env_roles_;
@@ -667,9 +752,9 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         shape->grid = static_cast<int>(lanes * 3);
         return GPUK_OK;
     }
-    int64_t grid = std::min<int64_t>(std::min<int64_t>(plan.grid, resident), nchunks);
-    if (grid < 1) grid = 1;
-    shape->grid = static_cast<int>(grid);
+    int64_t clusters = std::min<int64_t>(std::min<int64_t>(plan.grid, resident) / plan.cluster, nchunks);
+    if (clusters < 1) return fail(GPUK_ERR_UNSUPPORTED, "the GPU cannot hold one cluster of %d CTAs of the selected kernel", plan.cluster);
+    shape->grid = static_cast<int>(clusters * plan.cluster);
     return GPUK_OK;
 }
 
@@ -707,9 +792,20 @@ int gpuk_residual_rms_quant(const void *in, const void *residual_in, const void 
     p.in = in;
     p.rows = plan.rows;
     fill_epilogue(a, q, plan.row_vecs, &p.ep);
+    // many rows: the staged kernel (rows through shared memory by bulk copies); GPUK_K1_STAGES = 0
+    // switches it off, 2 or 3 picks the ring depth (tuning knob, read once)
+    static const int env_stages = [] { const char *e = getenv("GPUK_K1_STAGES"); return e ? atoi(e) : -1; }();
+    const int stages = env_stages < 0 ? kDefaultK1Stages : env_stages;
+    static const int env_staged_min = [] { const char *e = getenv("GPUK_K1_STAGED_MIN_ROWS_PER_SM"); return e ? atoi(e) : -1; }();
+    const bool staged = stages >= 2 && plan.rows >= static_cast<int64_t>(env_staged_min >= 0 ? env_staged_min : kK1StagedMinRowsPerSm) * sms;
     return by_dtype(dtype, [&](auto *t) {
         using T = std::remove_pointer_t<decltype(t)>;
-        cudaError_t e = launch_norm_quant<T>(p, plan.vpt, plan.threads, plan.grid, static_cast<cudaStream_t>(stream));
+        cudaError_t e = cudaErrorInvalidConfiguration;
+        if (staged) e = launch_norm_quant_staged<T>(p, plan.vpt, plan.threads, stages, sms, static_cast<cudaStream_t>(stream));
+        if (e == cudaErrorInvalidConfiguration) {
+            if (staged) cudaGetLastError();
+            e = launch_norm_quant<T>(p, plan.vpt, plan.threads, plan.grid, static_cast<cudaStream_t>(stream));
+        }
         if (e != cudaSuccess) return fail(GPUK_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
         return static_cast<int>(GPUK_OK);
     });

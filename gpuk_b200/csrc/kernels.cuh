@@ -1,6 +1,8 @@
 // The kernels of the tensor-parallel epilogue, written for sm_100a.
 //
 //   fused_norm_quant_kernel   one GPU, no communication: residual add + RMSNorm + FP8.
+//   fused_norm_quant_staged_kernel   the same for many rows, rows staged through shared memory
+//                             by bulk copies.
 //   ar_kernel                 N GPUs: all-reduce of the per-rank partials fused with the same
 //                             epilogue (or, with FUSED = false, a plain all-reduce), as a
 //                             one-shot (latency) or two-shot (bandwidth) exchange.
@@ -33,8 +35,8 @@
 //              communicator.h:82-88), and a CTA staggers its chunks: scatter k+1, reduce k,
 //              epilogue k-1.
 //
-// Staging is double-buffered by call parity (a device-side counter, so a replayed CUDA graph
-// stays in step): a rank can start call c+2 only after every peer has pushed its call c+1
+// Staging is double-buffered by call parity (a device-side counter that the kernel advances
+// itself, so a replayed CUDA graph stays in step): a rank can start call c+2 only after every peer has pushed its call c+1
 // data, i.e. after every peer's call c kernel -- including its consume-and-reset of buffer
 // c % 2 -- has completed.
 //
@@ -77,8 +79,61 @@ __global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>(
             const int v = threadIdx.x + i * blockDim.x;
             x[i] = v < p.ep.row_vecs ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
         }
-        load_residual<T, VPT>(p.ep, row, res);
-        row_epilogue<T, VPT>(p.ep, row, x, res, sm, parity, static_scale);
+        const RowSeg seg = whole_row(p.ep.row_vecs);
+        load_residual<T, VPT>(p.ep, seg, row, res);
+        row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
+    }
+}
+
+// The same operation for many rows: persistent CTAs take rows blockIdx.x, + gridDim.x, ... and
+// fetch each row (input and residual, contiguous in global memory) into a ring of STAGES
+// shared-memory stages with two bulk copies that one thread issues.  A stage is refilled with
+// the row STAGES ahead as soon as every thread has taken its vectors out of it, so the loads of
+// the next rows are in flight during both block reductions of the current one.
+// Dynamic shared memory: STAGES * 2 * row_vecs * 16 bytes.  Needs at least two warps per CTA
+// (the refill relies on the block barrier inside the first reduction).
+template <int VPT>
+constexpr int staged_min_blocks() { return VPT == 4 ? 3 : (VPT == 8 ? 1 : (VPT == 2 ? 1 : 1)); }
+
+template <typename T, int VPT, int STAGES>
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), staged_min_blocks<VPT>())
+    fused_norm_quant_staged_kernel(const __grid_constant__ NormQuantParams p) {
+    extern __shared__ __align__(128) unsigned char stage_mem[];
+    __shared__ EpilogueSmem sm;
+    __shared__ __align__(8) uint64_t full[STAGES];
+    const uint32_t row_bytes = static_cast<uint32_t>(p.ep.row_vecs) * 16u;
+    const int64_t nk = blockIdx.x < p.rows ? (p.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    auto issue = [&](int64_t k) {
+        const int s = static_cast<int>(k % STAGES);
+        const int64_t row = blockIdx.x + k * gridDim.x;
+        unsigned char *dst = stage_mem + static_cast<size_t>(s) * 2 * row_bytes;
+        mbar_expect_bytes(&full[s], 2 * row_bytes);
+        bulk_load(dst, static_cast<const unsigned char *>(p.in) + row * row_bytes, row_bytes, &full[s]);
+        bulk_load(dst + row_bytes, static_cast<const unsigned char *>(p.ep.residual) + row * row_bytes, row_bytes, &full[s]);
+    };
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+        mbar_init_fence();
+        for (int64_t k = 0; k < STAGES && k < nk; ++k) issue(k);
+    }
+    __syncthreads();
+    const float static_scale = p.ep.q.mode == kQuantStatic ? *p.ep.scale_out : 1.f;
+    const RowSeg seg = whole_row(p.ep.row_vecs);
+    for (int64_t k = 0; k < nk; ++k) {
+        const int s = static_cast<int>(k % STAGES);
+        mbar_wait(&full[s], static_cast<uint32_t>(k / STAGES) & 1u);
+        const uint4 *sx = reinterpret_cast<const uint4 *>(stage_mem + static_cast<size_t>(s) * 2 * row_bytes);
+        const uint4 *sr = sx + p.ep.row_vecs;
+        uint4 x[VPT], res[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * blockDim.x;
+            x[i] = v < p.ep.row_vecs ? sx[v] : make_uint4(0, 0, 0, 0);
+            res[i] = v < p.ep.row_vecs ? sr[v] : make_uint4(0, 0, 0, 0);
+        }
+        row_epilogue<T, VPT>(p.ep, seg, blockIdx.x + k * gridDim.x, x, res, sm, static_cast<int>(k & 1), static_scale,
+                             [&] { if (threadIdx.x == 0 && k + STAGES < nk) issue(k + STAGES); });
     }
 }
 
@@ -93,6 +148,9 @@ struct ArParams {
     int rows;
     int row_vecs;
     int rows_per_chunk;    // rows a CTA moves through one stage before it turns to the next stage
+    int seg_vecs;          // one-shot: vectors of a row held by one CTA of the cluster that owns the row
+    int lead_push;         // two-shot: chunks by which the scatter runs ahead of the reduction (>= 1)
+    int lead_reduce;       // two-shot: chunks by which the reduction runs ahead of the epilogue (>= 1)
     EpilogueArgs ep;       // fused only
     // communication
     int rank;
@@ -230,7 +288,8 @@ __device__ __noinline__ void finish_rows(const ArParams &p, int64_t ts, int r0, 
                 const int v = threadIdx.x + i * blockDim.x;
                 x[i] = v < p.row_vecs ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
             }
-            load_residual<T, VPT>(p.ep, row, res);
+            const RowSeg seg = whole_row(p.row_vecs);
+            load_residual<T, VPT>(p.ep, seg, row, res);
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = threadIdx.x + i * blockDim.x;
@@ -239,7 +298,7 @@ __device__ __noinline__ void finish_rows(const ArParams &p, int64_t ts, int r0, 
                     st_empty(ag + base + v);
                 }
             }
-            row_epilogue<T, VPT>(p.ep, row, x, res, sm, parity, static_scale);
+            row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
             parity ^= 1;
         } else {
             constexpr int U = 4;
@@ -265,10 +324,25 @@ __device__ __noinline__ void finish_rows(const ArParams &p, int64_t ts, int r0, 
 }
 
 // ---- the body: one CTA of one rank ------------------------------------------------------
+
+// Takes this CTA's ticket of the call and learns the call's number from the same atomic:
+// LocalState::seq holds the number of completed exchanges in its upper 16 bits (the low bit
+// of that number selects the staging buffer of this call) and the tickets taken so far by
+// CTAs of the running call in its lower 16 bits.  The CTA that takes the last ticket clears
+// the tickets and advances the number; every CTA of the call has read it by then, so the new
+// value is first seen by the next launch.  One thread does it and shares the number through
+// `sm.seq`; the caller passes a block barrier before reading it.
+__device__ __forceinline__ void begin_call(LocalState *st, int nb, EpilogueSmem &sm) {
+    if (threadIdx.x == 0) {
+        const uint32_t old = atomicAdd(&st->seq, 1u);
+        sm.seq = old >> 16;
+        if ((old & 0xffffu) == static_cast<uint32_t>(nb) - 1u) atomicAdd(&st->seq, 0x10000u - static_cast<uint32_t>(nb));
+    }
+}
+
 template <typename T, int NR, int VPT, bool TWO_SHOT, bool FUSED>
 __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, EpilogueSmem &sm) {
     LocalState *st = p.st;
-    const uint32_t buf = ld_volatile_u32(&st->seq) & 1u;   // staging is double-buffered by call parity
     float static_scale = 1.f;
     if constexpr (FUSED) {
         if (p.ep.q.mode == kQuantStatic) static_scale = *p.ep.scale_out;
@@ -277,53 +351,75 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
     const int R = p.rows_per_chunk;
     const int nchunks = (p.rows + R - 1) / R;
 
-    if (TWO_SHOT && p.roles == 3) {
-        // Specialised roles: the three stages of a lane's chunks run in three CTAs that meet only
-        // through the staging memory.
-        const int64_t ts = static_cast<int64_t>(buf) * p.ts_stride;
-        const int lanes = nb / 3, lane = vb / 3, role = vb - lane * 3;
-        const int nl = lane < nchunks ? (nchunks - lane + lanes - 1) / lanes : 0;
-        for (int k = 0; k < nl; ++k) {
-            const int r0 = (lane + k * lanes) * R;
-            const int r1 = r0 + R < p.rows ? r0 + R : p.rows;
-            if (role == 0) push_slices<T, NR>(p, ts, r0, r1);
-            else if (role == 1) reduce_and_gather<T, NR>(p, ts, r0, r1);
-            else finish_rows<T, NR, VPT, FUSED>(p, ts, r0, r1, sm, parity, static_scale);
+    if constexpr (TWO_SHOT) {
+        begin_call(st, nb, sm);
+        __syncthreads();
+        const int64_t ts = static_cast<int64_t>(sm.seq & 1u) * p.ts_stride;
+        if (p.roles == 3) {
+            // Specialised roles: the three stages of a lane's chunks run in three CTAs that meet
+            // only through the staging memory.
+            const int lanes = nb / 3, lane = vb / 3, role = vb - lane * 3;
+            const int nl = lane < nchunks ? (nchunks - lane + lanes - 1) / lanes : 0;
+            for (int k = 0; k < nl; ++k) {
+                const int r0 = (lane + k * lanes) * R;
+                const int r1 = r0 + R < p.rows ? r0 + R : p.rows;
+                if (role == 0) push_slices<T, NR>(p, ts, r0, r1);
+                else if (role == 1) reduce_and_gather<T, NR>(p, ts, r0, r1);
+                else finish_rows<T, NR, VPT, FUSED>(p, ts, r0, r1, sm, parity, static_scale);
+            }
+        } else {
+            // Every CTA takes its chunks (vb, vb + nb, ...) through all three stages as a software
+            // pipeline: in step s it scatters chunk s, reduces chunk s - lead_push and finishes
+            // chunk s - lead_push - lead_reduce, so that traffic for later chunks is on the wire
+            // while the epilogue of an earlier one runs.  No stage waits for anything but its own
+            // input vectors.
+            const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;
+            auto r0_of = [&](int k) { return (vb + k * nb) * R; };
+            auto r1_of = [&](int k) { const int r1 = (vb + k * nb) * R + R; return r1 < p.rows ? r1 : p.rows; };
+            // a lead beyond the CTA's own chunks means "finish the earlier stage first"
+            const int lp = p.lead_push < nk ? p.lead_push : nk, lr = p.lead_reduce < nk ? p.lead_reduce : nk;
+            const int steps = nk > 0 ? nk + lp + lr : 0;
+            for (int s = 0; s < steps; ++s) {
+                if (s < nk) push_slices<T, NR>(p, ts, r0_of(s), r1_of(s));
+                const int kr = s - lp;
+                if (kr >= 0 && kr < nk) reduce_and_gather<T, NR>(p, ts, r0_of(kr), r1_of(kr));
+                const int kf = kr - lr;
+                if (kf >= 0 && kf < nk) finish_rows<T, NR, VPT, FUSED>(p, ts, r0_of(kf), r1_of(kf), sm, parity, static_scale);
+            }
         }
-    } else if constexpr (TWO_SHOT) {
-        // Every CTA takes its chunks (vb, vb + nb, ...) through all three stages, staggered so
-        // that the scatter of chunk k+1 and the reduction of chunk k are on the wire while the
-        // epilogue of chunk k-1 runs.  No stage waits for anything but its own input vectors.
-        const int64_t ts = static_cast<int64_t>(buf) * p.ts_stride;
-        const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;
-        auto r0_of = [&](int k) { return (vb + k * nb) * R; };
-        auto r1_of = [&](int k) { const int r1 = (vb + k * nb) * R + R; return r1 < p.rows ? r1 : p.rows; };
-        if (nk > 0) push_slices<T, NR>(p, ts, r0_of(0), r1_of(0));
-        for (int k = 0; k < nk; ++k) {
-            if (k + 1 < nk) push_slices<T, NR>(p, ts, r0_of(k + 1), r1_of(k + 1));
-            reduce_and_gather<T, NR>(p, ts, r0_of(k), r1_of(k));
-            if (k > 0) finish_rows<T, NR, VPT, FUSED>(p, ts, r0_of(k - 1), r1_of(k - 1), sm, parity, static_scale);
-        }
-        if (nk > 0) finish_rows<T, NR, VPT, FUSED>(p, ts, r0_of(nk - 1), r1_of(nk - 1), sm, parity, static_scale);
     } else {
-        // one-shot: every rank receives every other rank's whole row and reduces it locally
-        const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;   // rows_per_chunk is 1 on this path
-        const int64_t bo = p.os_off + static_cast<int64_t>(buf) * NR * p.os_slot_bytes;
+        // one-shot: every rank receives every other rank's whole row and reduces it locally.  A
+        // row belongs to a cluster of CTAs, each of which exchanges and finishes one segment.
+        const int cl = cluster_size(), cr = cluster_cta_rank();
+        const int ncl = nb / cl, cid = vb / cl;
+        const int nk = cid < p.rows ? (p.rows - cid + ncl - 1) / ncl : 0;   // rows_per_chunk is 1 on this path
         const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
+        int64_t bo = 0;
         for (int k = 0; k < nk; ++k) {
-            const int row = vb + k * nb;
+            const int row = cid + k * ncl;
             const int len = row_len(p, row);
+            RowSeg seg;
+            seg.v0 = cr * p.seg_vecs;
+            seg.v1 = seg.v0 + p.seg_vecs < len ? seg.v0 + p.seg_vecs : len;
+            seg.cl_rank = cr;
+            seg.cl_size = cl;
             const int64_t rbase = static_cast<int64_t>(row) * p.row_vecs;
             uint4 x[VPT], res[VPT];
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * blockDim.x;
-                x[i] = v < len ? ld_stream(in + rbase + v) : make_uint4(0, 0, 0, 0);
+                const int v = seg.v0 + threadIdx.x + i * blockDim.x;
+                x[i] = v < seg.v1 ? ld_stream(in + rbase + v) : make_uint4(0, 0, 0, 0);
+            }
+            if (k == 0) {
+                // the counter is fetched while the first row's loads are in flight
+                begin_call(st, nb, sm);
+                __syncthreads();
+                bo = p.os_off + static_cast<int64_t>(sm.seq & 1u) * NR * p.os_slot_bytes;
             }
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * blockDim.x;
-                if (v < len) {
+                const int v = seg.v0 + threadIdx.x + i * blockDim.x;
+                if (v < seg.v1) {
                     const uint4 send = payload<T>(x[i]);
 #pragma unroll
                     for (int d = 1; d < NR; ++d) {
@@ -332,12 +428,12 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
                     }
                 }
             }
-            if constexpr (FUSED) load_residual<T, VPT>(p.ep, row, res);   // in flight while the peers' rows arrive
+            if constexpr (FUSED) load_residual<T, VPT>(p.ep, seg, row, res);   // in flight while the peers' rows arrive
             char *mine = p.peer_data[p.rank] + bo;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * blockDim.x;
-                if (v < len) {
+                const int v = seg.v0 + threadIdx.x + i * blockDim.x;
+                if (v < seg.v1) {
                     uint4 part[NR];
 #pragma unroll
                     for (int s = 0; s < NR; ++s)
@@ -354,28 +450,17 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
                 }
             }
             if constexpr (FUSED) {
-                row_epilogue<T, VPT>(p.ep, row, x, res, sm, parity, static_scale);
+                row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
                 parity ^= 1;
             } else {
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
-                    const int v = threadIdx.x + i * blockDim.x;
-                    if (v < len) st_stream(reinterpret_cast<uint4 *>(p.out) + rbase + v, x[i]);
+                    const int v = seg.v0 + threadIdx.x + i * blockDim.x;
+                    if (v < seg.v1) st_stream(reinterpret_cast<uint4 *>(p.out) + rbase + v, x[i]);
                 }
             }
         }
-    }
-
-    // the last CTA of this rank to finish flips the staging buffer for the next call
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const uint32_t done = atomicAdd(&st->ticket, 1u);
-        if (done == static_cast<uint32_t>(nb) - 1u) {
-            st->ticket = 0;
-            st->seq = st->seq + 1u;
-            __threadfence();
-        }
+        if (nk == 0) begin_call(st, nb, sm);   // a CTA without rows still takes its ticket
     }
 }
 

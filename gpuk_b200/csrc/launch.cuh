@@ -13,11 +13,24 @@ struct ArShape {
     bool two_shot;
     bool fused;
     int threads;
-    int grid;        // CTAs per rank
+    int grid;        // CTAs per rank (a multiple of `cluster`)
+    int cluster;     // CTAs per thread-block cluster (1: launched without a cluster attribute)
 };
+
+// Launches `fn` (one parameter block behind args) with an optional cluster dimension; with
+// `all_resident` the launch is cooperative, i.e. refused unless the whole grid fits the GPU.
+cudaError_t launch_kernel(const void *fn, int grid, int threads, int cluster, bool all_resident, void **args, cudaStream_t stream);
+// CTAs of `fn` that can be resident on the whole GPU at once, counting whole clusters only.
+cudaError_t resident_ctas(const void *fn, int threads, int cluster, int sm_count, int64_t *ctas);
 
 template <typename T>
 cudaError_t launch_norm_quant(const NormQuantParams &p, int vpt, int threads, int grid, cudaStream_t stream);
+
+// Staged variant (rows through shared memory by bulk copies).  `grid` <= 0 asks for one CTA per
+// resident slot of the GPU; returns cudaErrorInvalidConfiguration when the tile is not built or
+// a row does not fit the shared memory, so that the caller can use the plain kernel.
+template <typename T>
+cudaError_t launch_norm_quant_staged(const NormQuantParams &p, int vpt, int threads, int stages, int sm_count, cudaStream_t stream);
 
 template <typename T>
 cudaError_t launch_ar(const ArParams &p, const ArShape &s, cudaStream_t stream);
@@ -26,9 +39,9 @@ cudaError_t launch_ar(const ArParams &p, const ArShape &s, cudaStream_t stream);
 template <typename T>
 cudaError_t launch_ar_emulated(const ArParams *params_by_rank, const ArShape &s, cudaStream_t stream);
 
-// Resident CTAs per SM of the instantiation `s` selects (emulated = the one-GPU variant).
+// CTAs of the instantiation `s` selects that fit the GPU at once (emulated = the one-GPU variant).
 template <typename T>
-cudaError_t ar_blocks_per_sm(const ArShape &s, bool emulated, int *blocks_per_sm);
+cudaError_t ar_resident_ctas(const ArShape &s, bool emulated, int sm_count, int64_t *ctas);
 
 // Records the text gpuk_last_error() returns on this thread and hands `code` back
 // (defined next to gpuk_last_error).

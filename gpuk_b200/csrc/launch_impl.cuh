@@ -58,12 +58,49 @@ cudaError_t launch_norm_quant(const NormQuantParams &p, int vpt, int threads, in
     return cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, 0, stream);
 }
 
+template <typename T, int VPT, int STAGES>
+static cudaError_t launch_staged_one(const NormQuantParams &p, int threads, int sm_count, cudaStream_t stream) {
+    const void *fn = reinterpret_cast<const void *>(&fused_norm_quant_staged_kernel<T, VPT, STAGES>);
+    const size_t smem = static_cast<size_t>(STAGES) * 2 * p.ep.row_vecs * 16;
+    if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+    // per device: opt in to the shared-memory size and look up how many CTAs fit an SM
+    static int per_sm_by_device[64] = {};
+    static size_t smem_by_device[64] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device < 0 || device >= 64) return cudaErrorInvalidConfiguration;
+    if (per_sm_by_device[device] == 0 || smem_by_device[device] != smem) {
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        int per_sm = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, smem);
+        if (e != cudaSuccess) return e;
+        if (per_sm <= 0) return cudaErrorInvalidConfiguration;
+        per_sm_by_device[device] = per_sm;
+        smem_by_device[device] = smem;
+    }
+    const int64_t slots = static_cast<int64_t>(per_sm_by_device[device]) * sm_count;
+    const int grid = static_cast<int>(p.rows < slots ? p.rows : slots);
+    void *args[] = {const_cast<NormQuantParams *>(&p)};
+    return cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, smem, stream);
+}
+
+template <typename T>
+cudaError_t launch_norm_quant_staged(const NormQuantParams &p, int vpt, int threads, int stages, int sm_count, cudaStream_t stream) {
+    if (threads < 64) return cudaErrorInvalidConfiguration;
+    if (vpt == 4) return stages == 3 ? launch_staged_one<T, 4, 3>(p, threads, sm_count, stream) : launch_staged_one<T, 4, 2>(p, threads, sm_count, stream);
+    if (vpt == 2) return stages == 3 ? launch_staged_one<T, 2, 3>(p, threads, sm_count, stream) : launch_staged_one<T, 2, 2>(p, threads, sm_count, stream);
+    if (vpt == 1) return stages == 3 ? launch_staged_one<T, 1, 3>(p, threads, sm_count, stream) : launch_staged_one<T, 1, 2>(p, threads, sm_count, stream);
+    return cudaErrorInvalidConfiguration;
+}
+
 template <typename T>
 cudaError_t launch_ar(const ArParams &p, const ArShape &s, cudaStream_t stream) {
     const void *fn = ar_fn_any<T>(s, false);
     if (!fn) return cudaErrorInvalidValue;
     void *args[] = {const_cast<ArParams *>(&p)};
-    return cudaLaunchKernel(fn, dim3(s.grid), dim3(s.threads), args, 0, stream);
+    return launch_kernel(fn, s.grid, s.threads, s.cluster, false, args, stream);
 }
 
 template <typename T>
@@ -72,20 +109,21 @@ cudaError_t launch_ar_emulated(const ArParams *params_by_rank, const ArShape &s,
     if (!fn) return cudaErrorInvalidValue;
     int nb = s.grid;
     void *args[] = {&params_by_rank, &nb};
-    return cudaLaunchCooperativeKernel(fn, dim3(s.grid * s.world), dim3(s.threads), args, 0, stream);
+    return launch_kernel(fn, s.grid * s.world, s.threads, s.cluster, true, args, stream);
 }
 
 template <typename T>
-cudaError_t ar_blocks_per_sm(const ArShape &s, bool emulated, int *blocks_per_sm) {
+cudaError_t ar_resident_ctas(const ArShape &s, bool emulated, int sm_count, int64_t *ctas) {
     const void *fn = ar_fn_any<T>(s, emulated);
     if (!fn) return cudaErrorInvalidValue;
-    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, fn, s.threads, 0);
+    return resident_ctas(fn, s.threads, s.cluster, sm_count, ctas);
 }
 
 #define GPUK_INSTANTIATE_LAUNCHERS(T)                                                                          \
     template cudaError_t launch_norm_quant<T>(const NormQuantParams &, int, int, int, cudaStream_t);           \
+    template cudaError_t launch_norm_quant_staged<T>(const NormQuantParams &, int, int, int, int, cudaStream_t); \
     template cudaError_t launch_ar<T>(const ArParams &, const ArShape &, cudaStream_t);                        \
     template cudaError_t launch_ar_emulated<T>(const ArParams *, const ArShape &, cudaStream_t);               \
-    template cudaError_t ar_blocks_per_sm<T>(const ArShape &, bool, int *);
+    template cudaError_t ar_resident_ctas<T>(const ArShape &, bool, int, int64_t *);
 
 }  // namespace gpuk

@@ -76,7 +76,7 @@ __global__ void scratch_init_kernel(unsigned char *base, unsigned long long time
         LocalState *st = reinterpret_cast<LocalState *>(base + threadIdx.x * 256);
         st->seq = 0;
         st->reserved = 0;
-        st->ticket = 0;
+        st->reserved2 = 0;
         st->abort = 0;
         st->timeout_ns = timeout_ns;
         for (int i = 0; i < kStatusWords; ++i) st->status[i] = 0;
@@ -87,7 +87,6 @@ __global__ void scratch_clear_status_kernel(unsigned char *base, int world) {
     if (threadIdx.x < world) {
         LocalState *st = reinterpret_cast<LocalState *>(base + threadIdx.x * 256);
         st->abort = 0;
-        st->ticket = 0;
         for (int i = 0; i < kStatusWords; ++i) st->status[i] = 0;
     }
 }
@@ -202,13 +201,15 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
         base = d.base;
     }
 
-    // co-residency: all emulated ranks' CTAs wait for each other inside one cooperative launch
-    int per_sm = 0;
-    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, plan.threads, 0);
-    if (e != cudaSuccess || per_sm <= 0) return set_last_error(GPUK_ERR_CUDA, "selfcheck: occupancy query failed");
-    int64_t nb = static_cast<int64_t>(per_sm) * sms / world_size;
-    if (nb > plan.rows) nb = plan.rows;
-    if (nb < 1) return set_last_error(GPUK_ERR_UNSUPPORTED, "selfcheck: the GPU cannot hold one CTA per emulated rank");
+    // co-residency: all emulated ranks' CTAs wait for each other inside one launch
+    int64_t resident = 0;
+    cudaError_t e = resident_ctas(fn, plan.threads, plan.cluster, sms, &resident);
+    if (e != cudaSuccess || resident <= 0) return set_last_error(GPUK_ERR_CUDA, "selfcheck: occupancy query failed");
+    int64_t clusters = resident / world_size / plan.cluster;
+    if (clusters > plan.rows) clusters = plan.rows;
+    if (clusters > plan.grid / plan.cluster) clusters = plan.grid / plan.cluster;
+    if (clusters < 1) return set_last_error(GPUK_ERR_UNSUPPORTED, "selfcheck: the GPU cannot hold one cluster per emulated rank");
+    const int64_t nb = clusters * plan.cluster;
 
     const int es = dtype == GPUK_DTYPE_F32 ? 4 : 2;
     EmulatedParams ep;
@@ -227,6 +228,9 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
         p.rows = plan.rows;
         p.row_vecs = plan.row_vecs;
         p.rows_per_chunk = 1;
+        p.seg_vecs = (plan.row_vecs + plan.cluster - 1) / plan.cluster;
+        p.lead_push = plan.lead_push > 0 ? plan.lead_push : 1;
+        p.lead_reduce = plan.lead_reduce > 0 ? plan.lead_reduce : 1;
         p.ep.residual = residual_in;
         p.ep.gamma = rms_gamma;
         p.ep.residual_out = residual_out[r];
@@ -251,7 +255,7 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
     scratch_clear_status_kernel<<<1, 32, 0, s>>>(base, world_size);
     int nb_arg = static_cast<int>(nb);
     void *args[] = {&ep, &nb_arg};
-    e = cudaLaunchCooperativeKernel(fn, dim3(static_cast<unsigned>(nb * world_size)), dim3(plan.threads), args, 0, s);
-    if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "selfcheck: cooperative launch failed: %s", cudaGetErrorString(e));
+    e = launch_kernel(fn, static_cast<int>(nb * world_size), plan.threads, plan.cluster, true, args, s);
+    if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "selfcheck: launch failed: %s", cudaGetErrorString(e));
     return GPUK_OK;
 }

@@ -186,6 +186,9 @@ typedef struct gpuk_plan {
     int rows;
     int row_vecs;
     int64_t message_bytes;
+    int cluster;        /* CTAs (one thread-block cluster) that share a row; 1 unless few rows must fill the GPU */
+    int lead_push;      /* two-shot pipeline: chunks the scatter runs ahead of the reduction */
+    int lead_reduce;    /* two-shot pipeline: chunks the reduction runs ahead of the epilogue */
 } gpuk_plan;
 
 /*

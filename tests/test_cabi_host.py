@@ -50,11 +50,13 @@ def test_argument_validation_precedes_cuda():
 def test_plan_benchmark_configs():
     sms = 148
     c2 = cabi.plan(8, 8 * 8192, 8192, sm_count=sms)
-    assert c2.one_shot == 1 and c2.grid == 8 and c2.rows == 8 and c2.row_vecs == 1024
-    assert c2.vpt * c2.threads >= c2.row_vecs
+    # eight rows are spread over the GPU: each row is held by a cluster of eight CTAs
+    assert c2.one_shot == 1 and c2.rows == 8 and c2.row_vecs == 1024 and c2.cluster == 8 and c2.grid == 64
+    assert c2.vpt * c2.threads * c2.cluster >= c2.row_vecs and c2.threads == 128
     c3 = cabi.plan(8, 1024 * 8192, 8192, sm_count=sms)
     assert c3.one_shot == 0 and c3.message_bytes == 16 << 20
-    assert c3.grid * c3.rows_per_chunk <= 1024 and c3.grid <= 2048
+    assert c3.grid * c3.rows_per_chunk <= 1024 and c3.grid <= 2048 and c3.cluster == 1
+    assert c3.lead_push >= 1 and c3.lead_reduce >= 1
     c4 = cabi.plan(8, 16384 * 7168, 7168, sm_count=sms)
     assert c4.one_shot == 0 and c4.row_vecs == 896 and c4.vpt * c4.threads >= 896 and c4.threads % 32 == 0
     c5 = cabi.plan(8, 32 * 8192, 8192, sm_count=sms)
@@ -86,4 +88,5 @@ def test_plan_tiles_cover_every_legal_row():
     for hidden in range(8, 32768 + 1, 8 * 37):
         p = cabi.plan(8, 4 * hidden, hidden)
         assert p.vpt in (1, 2, 4, 8) and p.threads % 32 == 0 and p.threads <= (512 if p.vpt >= 4 else 1024)
-        assert p.vpt * p.threads >= p.row_vecs == hidden // 8
+        assert p.cluster in (1, 2, 4, 8) and p.grid % p.cluster == 0
+        assert p.vpt * p.threads * p.cluster >= p.row_vecs == hidden // 8

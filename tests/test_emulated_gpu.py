@@ -50,11 +50,15 @@ def test_fused_other_dtypes(dtype, mode):
 
 
 @pytest.mark.parametrize("world", [2, 8])
-def test_two_shot_many_chunks_per_cta(world):
-    """More rows than resident CTAs: every CTA pipelines several chunks (push k+1, reduce k,
-    epilogue k-1), the regime of the prefill benchmark."""
+@pytest.mark.parametrize("lead_push,lead_reduce", [(0, 0), (2, 3), (100000, 100000)])
+def test_two_shot_many_chunks_per_cta(world, lead_push, lead_reduce):
+    """More rows than resident CTAs: every CTA pipelines several chunks (scatter s, reduce
+    s - lead_push, epilogue s - lead_push - lead_reduce), the regime of the prefill benchmark;
+    0 keeps the default depths, the huge value runs the three stages strictly one after another."""
     parts, res, w = util.random_case(world, 1500, 1024, torch.bfloat16, seed=5 + world)
     with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        g.set_option("lead_push", lead_push)
+        g.set_option("lead_reduce", lead_reduce)
         outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, 3, force_mode=TWO_SHOT)
     want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
     _check_all_ranks(outs, want, 3)
@@ -124,6 +128,24 @@ def test_plain_allreduce_f32():
         outs = g.plain([p.cuda() for p in parts], force_mode=TWO_SHOT)
     for got in outs:
         torch.testing.assert_close(got, want, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("tokens,hidden,quant", [(1, 8192, 3), (3, 2056, 3), (20, 4096, 4), (40, 8192, 1), (70, 7168, 0)])
+def test_one_shot_rows_split_over_a_cluster(world, tokens, hidden, quant):
+    """Few rows: each row is exchanged and normalised by a thread-block cluster (the two row-wide
+    reductions cross CTAs); called twice so that the staging double buffer and the call counter
+    advance, and with a ragged split (2056 / 8 = 257 vectors over two CTAs)."""
+    from gpuk_b200 import cabi
+    plan = cabi.plan(world, tokens * hidden, hidden, oneshot_max_bytes=2 << 20)
+    assert plan.one_shot == 1 and plan.cluster > 1
+    static = 0.05 if quant == 4 else None
+    with util.EmulatedGroup(world) as g:
+        for call in range(2):
+            parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 31 + tokens + call)
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=ONE_SHOT)
+            want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
+            _check_all_ranks(outs, want, quant)
 
 
 def test_benchmark_decode_config_eight_ranks():

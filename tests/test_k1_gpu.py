@@ -43,6 +43,18 @@ def test_shapes_dtypes_policies(tokens, hidden, quant, dtype):
     util.check_against_oracle(got, want, quant)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("quant", [0, 3, 4])
+@pytest.mark.parametrize("tokens,hidden", [(2368, 1024), (5000, 2048), (2400, 8192), (2501, 7168), (3000, 136)])
+def test_many_rows_staged_through_shared_memory(tokens, hidden, quant, dtype):
+    """Row counts from sixteen times the SM count up run on persistent CTAs that fetch rows into a
+    shared-memory ring with bulk copies: ring wrap-around (several rows per CTA), a ragged last
+    round, rows whose size is not a power of two, and a narrow row (two warps per CTA)."""
+    parts, res, w = util.random_case(1, tokens, hidden, dtype, seed=tokens + hidden + quant)
+    got, want = _run(parts[0], res, w, 1e-6, quant, 0.05 if quant == 4 else None)
+    util.check_against_oracle(got, want, quant, exact_residual=True)
+
+
 def test_long_rows():
     for hidden in (16384, 32768):
         parts, res, w = util.random_case(1, 4, hidden, torch.bfloat16, seed=hidden)
