@@ -387,6 +387,36 @@ def reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_crossover(env, gpuk, rank, world, barrier, hidden=8192):
+    """Microseconds per call (CUDA graph replay of the rotating buffer sets) of the three exchanges over
+    the token counts between decode and prefill; used to place the thresholds between them."""
+    from gpuk_b200 import workloads as oin
+    rows = []
+    have_sym = getattr(env, "_sym", None) is not None
+    for tokens in (1, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192):
+        cfg = oin.Config(9, f"x_{tokens}x{hidden}", tokens, hidden, 3)
+        entry = {"tokens": tokens, "bytes": tokens * hidden * 2}
+        for name, opts in (("one_shot", {"oneshot_max_bytes": 1 << 40, "sym_min_bytes": 0}),
+                           ("two_shot", {"oneshot_max_bytes": 1, "sym_min_bytes": 0}),
+                           ("symmetric", {"oneshot_max_bytes": 1, "sym_min_bytes": 1})):
+            if name == "one_shot" and tokens * hidden * 2 > (2 << 20):
+                continue
+            if name == "symmetric" and not have_sym:
+                continue
+            for k, v in opts.items():
+                env.set_option(k, v)
+            steps = 400 if tokens <= 256 else (100 if tokens <= 2048 else 30)
+            try:
+                r = run_config(cfg, env, gpuk, rank, world, steps, 5, barrier, graph=True)
+                entry[name] = r.get("us_per_call_graph", r["us_per_call"])
+            except Exception as e:
+                entry[name] = repr(e)[:120]
+        rows.append(entry)
+    env.set_option("oneshot_max_bytes", 0)
+    env.set_option("sym_min_bytes", int(os.environ.get("GPUK_SYM_MIN_BYTES", "0")))
+    return rows
+
+
 # ---------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -398,6 +428,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-model", action="store_true", help="skip the decoder-model step (config 5) in the sweep")
+    ap.add_argument("--crossover", action="store_true", help="also time one-shot / two-shot / symmetric over token counts")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -458,6 +489,8 @@ def main():
             except Exception as e:
                 sweep.append({"workload": "c5_decoder", "error": repr(e)[:300]})
 
+    crossover = run_crossover(env, gpuk, rank, world, barrier) if (args.crossover and world > 1) else None
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         us, cores, threads = cpu_reference_us(args.workload, 1, 12, 3)
@@ -493,6 +526,8 @@ def main():
             "us_per_call_graph": head.get("us_per_call_graph"),
             "cpu_baseline": cpu, "sweep": sweep,
         }
+        if crossover is not None:
+            line["crossover"] = crossover
         print(json.dumps(line), flush=True)
     barrier()
     del env

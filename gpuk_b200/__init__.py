@@ -108,13 +108,19 @@ class GPUKDistEnv:
       per-tensor scale instead of per-token dynamic scales) and ``quant_type`` (override of
       the module-level FP8 policy);
     * inputs are never registered or copied into staging by the host, so ``capture`` /
-      ``consume_capture`` exchange nothing (they still synchronise the group as before).
+      ``consume_capture`` exchange nothing (they still synchronise the group as before);
+    * ``symmetric_bytes`` (keyword-only, or ``GPUK_SYMMETRIC_BYTES``) adds a second exchange for
+      large messages: a buffer of that size from ``torch.distributed._symmetric_memory`` is
+      attached to the workspace, and where the NVSwitch offers a multicast mapping the reduction
+      runs inside the switch.  ``set_option("sym_min_bytes", n)`` sends fused calls of at least
+      ``n`` bytes through it.
     """
 
     _SUPPORTED_WORLD_SIZES = [2, 4, 8]
 
     def __init__(self, group=None, device_id: int = None, max_size_in_bytes=16384 * 16384,
-                 comm_ptrs_buf_len=1024 * 256, dtype: torch.dtype = torch.bfloat16, *, _ops=None) -> None:
+                 comm_ptrs_buf_len=1024 * 256, dtype: torch.dtype = torch.bfloat16, *, symmetric_bytes: Optional[int] = None,
+                 _ops=None) -> None:
         self._o = _ops or _TorchOps
         self.group = group
         self.device_id = device_id
@@ -143,6 +149,34 @@ class GPUKDistEnv:
         self._o.open_ar_fusion_barrier_handles(self.fptr, barrier_handle_list)
         self._o.open_ar_fusion_data_handles(self.fptr, data_handle_list)
         self.barrier()
+        self.multicast = False
+        if symmetric_bytes is None and os.environ.get("GPUK_SYMMETRIC_BYTES"):
+            symmetric_bytes = int(os.environ["GPUK_SYMMETRIC_BYTES"])
+        if symmetric_bytes:
+            self._attach_symmetric(int(symmetric_bytes))
+
+    def _attach_symmetric(self, nbytes: int) -> None:
+        """Allocates this rank's symmetric buffer, maps the peers' (and the multicast address where
+        the fabric has one) and hands the addresses to the workspace."""
+        import ctypes
+        import torch.distributed._symmetric_memory as symm
+        nbytes = (nbytes + 255) // 256 * 256
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._sym = symm.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", self.device_id))
+        self._sym.zero_()
+        self._sym_handle = symm.rendezvous(self._sym, group.group_name)
+        bases = (ctypes.c_void_p * self.world_size)(*[int(p) for p in self._sym_handle.buffer_ptrs])
+        mc = int(getattr(self._sym_handle, "multicast_ptr", 0) or 0)
+        cabi.check(cabi.lib.gpuk_ws_attach_symmetric(ctypes.c_void_p(self.fptr), bases, self.world_size,
+                                                     ctypes.c_void_p(mc) if mc else None, nbytes))
+        self.multicast = bool(mc)
+        self.barrier()
+
+    def set_option(self, name: str, value: int) -> None:
+        """Tuning options of the workspace (``gpuk_ws_set_option``); every rank must set the same."""
+        import ctypes
+        if self.fptr:
+            cabi.check(cabi.lib.gpuk_ws_set_option(ctypes.c_void_p(self.fptr), name.encode(), int(value)))
 
     def barrier(self):
         self._o.set_device(self.device_id)

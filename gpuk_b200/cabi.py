@@ -17,6 +17,8 @@ OK, ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOT_READY, ERR_TOO_LARG
 DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
 QUANT_NONE, QUANT_FP8_E4M3FN_240, QUANT_FP8_E4M3FNUZ_120, QUANT_FP8_E4M3FN_448, QUANT_FP8_E4M3FN_448_STATIC = range(5)
 IPC_HANDLE_BYTES = 64
+MODE_AUTO, MODE_ONE_SHOT, MODE_TWO_SHOT, MODE_SYMMETRIC = range(4)
+SYM_FLAG_BYTES = 2 * 2048 * 8 * 8   # tail of a symmetric buffer that holds the flags (include/gpuk_b200.h)
 
 
 class Plan(ctypes.Structure):
@@ -49,6 +51,7 @@ _SIGNATURES = {
     "gpuk_ws_open_data_handles": (c_int, [_P, POINTER(c_uint8), c_int]),
     "gpuk_ws_local_pointers": (c_int, [_P, POINTER(_P), POINTER(_P)]),
     "gpuk_ws_set_peer_pointers": (c_int, [_P, POINTER(_P), POINTER(_P), c_int]),
+    "gpuk_ws_attach_symmetric": (c_int, [_P, POINTER(_P), c_int, _P, c_int64]),
     "gpuk_enable_peer_access": (c_int, [c_int]),
     "gpuk_ws_capture_clear": (c_int, [_P]),
     "gpuk_ws_captured_count": (c_int, [_P, POINTER(c_int)]),

@@ -33,9 +33,8 @@ struct Quant {
 // device-resident state of one rank's workspace (local, never mapped by peers)
 // ---------------------------------------------------------------------------------------
 struct LocalState {
-    uint32_t seq;         // bits 31..16: exchanges completed so far (the low bit of that number selects the
-                          // staging buffer of the next one); bits 15..0: tickets taken by CTAs of the running call
-    uint32_t reserved;
+    unsigned long long seq;   // bits 63..16: exchanges completed so far (the low bit of that number selects the
+                              // staging buffer of the next one); bits 15..0: tickets taken by CTAs of the running call
     uint32_t reserved2;
     uint32_t abort;       // set once a wait has run out, so that later waits give up at once
     unsigned long long timeout_ns;
@@ -43,7 +42,7 @@ struct LocalState {
 };
 
 // stage codes in status[3]
-enum Stage : int { kStageOneShot = 0, kStageScatter = 1, kStageGather = 2, kStageSelfTest = 3 };
+enum Stage : int { kStageOneShot = 0, kStageScatter = 1, kStageGather = 2, kStageSelfTest = 3, kStageSymIn = 4, kStageSymOut = 5 };
 
 enum StatusCode : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusSpinCap = 2 };
 
@@ -270,6 +269,17 @@ __device__ __forceinline__ float block_max(float v, float *sm) {
 }
 
 // ---------------------------------------------------------------------------------------
+// programmatic dependent launch: the first statement of every kernel that is launched with
+// the programmatic-serialization attribute.  Waits until the preceding grid of the stream has
+// completed and its writes are visible (a no-op in an ordinary launch), then lets the grid
+// that follows begin to place its CTAs, which will wait here in their turn.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------
 // bulk copies (the TMA unit without a tensor map): whole rows travel from global to shared
 // memory asynchronously and announce their arrival on an mbarrier, so a CTA keeps loads in
 // flight while it computes.  Source, destination and size must be multiples of 16 bytes.
@@ -417,6 +427,53 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
+// ---------------------------------------------------------------------------------------
+// exchange through symmetric memory: NVSwitch multicast (multimem) and 64-bit flags
+// ---------------------------------------------------------------------------------------
+// A multicast address names the same offset in every rank's symmetric buffer.  A multimem load
+// with reduction returns the sum of that location over all ranks, added up inside the switch
+// (fp32 accumulation for the 16-bit types, one rounding); a multimem store writes all ranks.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_ld_sum(const void *mc);
+template <>
+__device__ __forceinline__ uint4 multimem_ld_sum<__nv_bfloat16>(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_sum<__half>(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_sum<float>(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_st(void *mc, const uint4 &v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// Flag stores with release semantics (after a block barrier and a system fence they publish the
+// CTA's earlier writes), to one rank or through the multicast address to all of them.
+__device__ __forceinline__ void st_flag_release(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_st_flag_release(unsigned long long *mc, unsigned long long v) {
+    asm volatile("multimem.st.release.sys.global.u64 [%0], %1;" ::"l"(mc), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_flag_acquire(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 constexpr uint32_t kSpinCap = 1u << 24;   // hard bound on polls of one wait, independent of the timer
 
 __device__ __forceinline__ void record_status(LocalState *st, uint32_t code, int rank, int block, int stage,
@@ -458,6 +515,30 @@ static __device__ __noinline__ uint4 wait_landed_slow(const void *addr, uint4 v,
 }
 __device__ __forceinline__ uint4 wait_landed(const void *addr, uint4 v, LocalState *st, int rank, int stage, int peer) {
     return landed(v) ? v : wait_landed_slow(addr, v, st, rank, stage, peer);
+}
+
+// Polls a flag until it has reached `want` (flags only grow), with the same bounds and the same
+// reporting as wait_landed.  Returns false when it gave up.
+static __device__ __noinline__ bool wait_flag(const unsigned long long *flag, unsigned long long want, LocalState *st, int rank,
+                                              int stage, int peer) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it <= kSpinCap; ++it) {
+        const unsigned long long seen = ld_flag_acquire(flag);
+        if (seen >= want) return true;
+        if ((it & 63u) == 63u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+                if (ld_volatile_u32(&st->abort)) return false;
+            } else if (now - t0 > st->timeout_ns || ld_volatile_u32(&st->abort)) {
+                record_status(st, kStatusWaitTimeout, rank, blockIdx.x, stage, peer, static_cast<uint32_t>(seen));
+                return false;
+            }
+        }
+        __nanosleep(20);
+    }
+    record_status(st, kStatusSpinCap, rank, blockIdx.x, stage, peer, 0u);
+    return false;
 }
 
 }  // namespace gpuk

@@ -61,27 +61,37 @@ int gpuk::set_last_error(int code, const char *fmt, ...) {
 }
 
 cudaError_t gpuk::launch_kernel(const void *fn, int grid, int threads, int cluster, bool all_resident, void **args,
-                                cudaStream_t stream) {
-    if (cluster <= 1) {
-        return all_resident ? cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(threads), args, 0, stream)
-                            : cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, 0, stream);
-    }
+                                cudaStream_t stream, size_t dynamic_smem) {
+    static const bool pdl = [] { const char *e = getenv("GPUK_PDL"); return !e || atoi(e) != 0; }();
+    if (cluster <= 1 && all_resident) return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(threads), args, dynamic_smem, stream);
+    if (cluster <= 1 && !pdl) return cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, dynamic_smem, stream);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(threads);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = dynamic_smem;
     cfg.stream = stream;
     cudaLaunchAttribute attrs[2];
-    attrs[0].id = cudaLaunchAttributeClusterDimension;
-    attrs[0].val.clusterDim.x = cluster;
-    attrs[0].val.clusterDim.y = 1;
-    attrs[0].val.clusterDim.z = 1;
-    attrs[1].id = cudaLaunchAttributeCooperative;
-    attrs[1].val.cooperative = 1;
+    int n = 0;
+    if (cluster > 1) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = cluster;
+        attrs[n].val.clusterDim.y = 1;
+        attrs[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (all_resident) {
+        attrs[n].id = cudaLaunchAttributeCooperative;
+        attrs[n].val.cooperative = 1;
+        ++n;
+    } else if (pdl) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     cfg.attrs = attrs;
-    cfg.numAttrs = all_resident ? 2 : 1;
+    cfg.numAttrs = n;
     cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
-    if (e != cudaSuccess && all_resident && e != cudaErrorCooperativeLaunchTooLarge) {
+    if (e != cudaSuccess && all_resident && cluster > 1 && e != cudaErrorCooperativeLaunchTooLarge) {
         // The cooperative attribute was not accepted together with a cluster.  The callers of
         // all_resident launches size the grid with resident_ctas() and every wait in the kernels
         // is bounded, so the launch goes ahead without it.
@@ -151,9 +161,10 @@ int elem_size(int dtype) {
 bool valid_world(int w) { return w == 2 || w == 4 || w == 8; }
 
 int64_t default_oneshot_max_bytes(int world) {
-    // Starting point before measurement: reference rule impl.h:375-376 scaled up for NVLink 5.
+    // The reference's rule is impl.h:375-376.  Two ranks: measured, one-shot wins up to the largest
+    // one-shot slot (10.0 vs 13.5 us at 2 MiB); four and eight ranks: see the crossover table of the bench.
     switch (world) {
-    case 2: return 1 << 20;
+    case 2: return 2 << 20;
     case 4: return 512 << 10;
     default: return 256 << 10;
     }
@@ -224,6 +235,12 @@ struct gpuk_ws {
     int64_t oneshot_max_bytes = 0;
     int opt_roles = 0, opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default / environment
     int opt_lead_push = 0, opt_lead_reduce = 0;
+    // exchange through symmetric memory (gpuk_ws_attach_symmetric)
+    char *sym[kMaxRanks] = {};
+    char *sym_mc = nullptr;
+    int64_t sym_cap = 0, sym_flag_off = 0;   // largest message; offset of the flags
+    int64_t sym_min_bytes = 0;               // messages from this size take it (0: never automatically)
+    bool sym_use_mc = true;                  // reduce inside the switch where a multicast mapping exists
     std::map<uint32_t, int64_t> occupancy;   // CTAs resident on the whole GPU, by kernel instantiation
 };
 
@@ -456,6 +473,25 @@ int gpuk_ws_set_peer_pointers(gpuk_ws *ws, void *const *flags, void *const *data
     return GPUK_OK;
 }
 
+int gpuk_ws_attach_symmetric(gpuk_ws *ws, void *const *bases, int n, void *mc_base, int64_t bytes) {
+    if (!ws || !bases) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace or buffer table");
+    if (n != ws->world) return fail(GPUK_ERR_INVALID_ARGUMENT, "expected %d buffers, got %d", ws->world, n);
+    if (bytes < kSymFlagBytes + 512) return fail(GPUK_ERR_INVALID_ARGUMENT, "symmetric buffer of %lld bytes is too small", (long long)bytes);
+    for (int r = 0; r < n; ++r)
+        if (!bases[r] || (reinterpret_cast<uintptr_t>(bases[r]) & 255u))
+            return fail(GPUK_ERR_INVALID_ARGUMENT, "symmetric buffer of rank %d is null or not 256-byte aligned", r);
+    if (reinterpret_cast<uintptr_t>(mc_base) & 255u) return fail(GPUK_ERR_INVALID_ARGUMENT, "multicast mapping is not 256-byte aligned");
+    for (int r = 0; r < n; ++r) ws->sym[r] = static_cast<char *>(bases[r]);
+    ws->sym_mc = static_cast<char *>(mc_base);
+    ws->sym_cap = (bytes - kSymFlagBytes) / 2 / 256 * 256;
+    ws->sym_flag_off = 2 * ws->sym_cap;
+    static const int64_t env_min = [] { const char *e = getenv("GPUK_SYM_MIN_BYTES"); return e ? atoll(e) : 0ll; }();
+    if (env_min > 0) ws->sym_min_bytes = env_min;
+    static const int env_mc = [] { const char *e = getenv("GPUK_SYM_MULTICAST"); return e ? atoi(e) : 1; }();
+    ws->sym_use_mc = env_mc != 0;
+    return GPUK_OK;
+}
+
 int gpuk_enable_peer_access(int n_devices) {
     int count = 0;
     GPUK_CUDA(cudaGetDeviceCount(&count));
@@ -555,6 +591,12 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     } else if (n == "lead_push" || n == "lead_reduce") {
         if (value < 0 || value > (1 << 20)) return fail(GPUK_ERR_INVALID_ARGUMENT, "%s must be in [0, 2^20]", name);
         (n == "lead_push" ? ws->opt_lead_push : ws->opt_lead_reduce) = static_cast<int>(value);
+    } else if (n == "sym_multicast") {
+        if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "sym_multicast must be 0 or 1");
+        ws->sym_use_mc = value != 0;
+    } else if (n == "sym_min_bytes") {
+        if (value < 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "sym_min_bytes must not be negative");
+        ws->sym_min_bytes = value;
     } else if (n == "oneshot_max_bytes") {
         return gpuk_ws_set_oneshot_max_bytes(ws, value);
     } else {
@@ -669,6 +711,18 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         return fail(GPUK_ERR_TOO_LARGE, "message of %lld bytes exceeds the workspace (%lld bytes)",
                     (long long)plan.message_bytes, (long long)ws->cap);
     bool one_shot = plan.one_shot != 0;
+    int sym = 0;
+    if (force_mode == GPUK_MODE_SYMMETRIC ||
+        (force_mode == GPUK_MODE_AUTO && fused && !one_shot && ws->sym[ws->rank] && ws->sym_min_bytes > 0 &&
+         plan.message_bytes >= ws->sym_min_bytes && plan.message_bytes <= ws->sym_cap)) {
+        if (!fused) return fail(GPUK_ERR_UNSUPPORTED, "the exchange through symmetric memory is built for the fused operator only");
+        if (!ws->sym[ws->rank]) return fail(GPUK_ERR_NOT_READY, "no symmetric memory attached to this workspace");
+        if (plan.message_bytes > ws->sym_cap)
+            return fail(GPUK_ERR_TOO_LARGE, "message of %lld bytes exceeds the symmetric buffer (%lld bytes per message)",
+                        (long long)plan.message_bytes, (long long)ws->sym_cap);
+        sym = (ws->sym_mc && ws->sym_use_mc && !emulated) ? 2 : 1;
+        force_mode = GPUK_MODE_TWO_SHOT;
+    }
     if (force_mode == 1) {
         if (plan.message_bytes > ws->os_slot_bytes || plan.rows > kMaxBlocks)
             return fail(GPUK_ERR_TOO_LARGE, "message too large for the one-shot path");
@@ -708,7 +762,12 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     p->ts_stride = ws->ts_stride;
     p->os_off = ws->os_off;
     p->os_slot_bytes = ws->os_slot_bytes;
-    if (!one_shot && static_cast<int64_t>(plan.rows) * p->vpr * 16 > ws->rs_slot_bytes)
+    for (int r = 0; r < ws->world; ++r) p->sym[r] = ws->sym[r];
+    p->sym_mc = ws->sym_mc;
+    p->sym_in_off = 0;
+    p->sym_out_off = ws->sym_cap;
+    p->sym_flag_off = ws->sym_flag_off;
+    if (!one_shot && !sym && static_cast<int64_t>(plan.rows) * p->vpr * 16 > ws->rs_slot_bytes)
         return fail(GPUK_ERR_TOO_LARGE, "message does not fit the reduce-scatter slots of the workspace");
 
     shape->world = ws->world;
@@ -718,10 +777,11 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     shape->threads = plan.threads;
     shape->cluster = plan.cluster;
     shape->grid = plan.grid;
+    shape->sym = sym;
     // the grid must be co-resident: CTAs of equal index on different ranks wait for each other
     const uint32_t key = static_cast<uint32_t>(a.dtype) | (plan.vpt << 4) | (one_shot ? 1u << 8 : 0u) |
                          (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (static_cast<uint32_t>(plan.threads) << 12) |
-                         (static_cast<uint32_t>(plan.cluster) << 24);
+                         (static_cast<uint32_t>(plan.cluster) << 24) | (static_cast<uint32_t>(sym) << 28);
     int64_t resident = 0;
     auto cached = ws->occupancy.find(key);
     if (cached != ws->occupancy.end()) {
@@ -743,7 +803,7 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     const int64_t nchunks = (static_cast<int64_t>(plan.rows) + plan.rows_per_chunk - 1) / plan.rows_per_chunk;
     static const int env_roles_ = [] { const char *e = getenv("GPUK_ROLES"); return e ? atoi(e) : 0; }();
     const int env_roles = ws->opt_roles ? ws->opt_roles : env_roles_;
-    const int roles = (!one_shot && (env_roles == 3 || (env_roles == 0 && kDefaultRoles == 3)) && resident >= 3) ? 3 : 1;
+    const int roles = (!one_shot && !sym && (env_roles == 3 || (env_roles == 0 && kDefaultRoles == 3)) && resident >= 3) ? 3 : 1;
     p->roles = roles;
     if (roles == 3) {
         // lanes of three specialised CTAs; flag rows are indexed by lane
@@ -862,7 +922,7 @@ int gpuk_emulated_allreduce_rms(gpuk_ws *const *wss, int world_size, void *const
         int rc = build_ar_call(ws, a, force_mode, true, &host_params[r], &s);
         if (rc) return rc;
         if (r == 0) shape = s;
-        else if (s.grid != shape.grid || s.threads != shape.threads || s.vpt != shape.vpt || s.two_shot != shape.two_shot)
+        else if (s.grid != shape.grid || s.threads != shape.threads || s.vpt != shape.vpt || s.two_shot != shape.two_shot || s.sym != shape.sym)
             return fail(GPUK_ERR_INVALID_ARGUMENT, "ranks disagree on the launch shape");
     }
     gpuk_ws *w0 = wss[0];

@@ -53,7 +53,7 @@ __device__ __forceinline__ RowSeg whole_row(int row_vecs) { return RowSeg{0, row
 struct alignas(16) EpilogueSmem {
     float red[2][2][32];
     float cl[2][2][8];
-    uint32_t seq;        // call counter of the exchange, read once per CTA (ar_body)
+    unsigned long long seq;   // number of the running exchange, fetched once per CTA (begin_call)
 };
 
 // The RMSNorm weight is re-read for every row (it stays in L1/L2) instead of being held in

@@ -6,6 +6,9 @@
 //   ar_kernel                 N GPUs: all-reduce of the per-rank partials fused with the same
 //                             epilogue (or, with FUSED = false, a plain all-reduce), as a
 //                             one-shot (latency) or two-shot (bandwidth) exchange.
+//   ar_sym_kernel             N GPUs, bandwidth regime: the exchange through symmetric memory,
+//                             reduced inside the NVSwitch (multimem) where a multicast mapping
+//                             exists; fused with the same epilogue.
 //   ar_emulated_kernel        the same device code run for N ranks inside ONE cooperative
 //                             launch on one GPU, so that the multi-rank logic can be checked
 //                             where only one GPU is available.
@@ -69,6 +72,7 @@ template <typename T, int VPT>
 __global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>())
     fused_norm_quant_kernel(const __grid_constant__ NormQuantParams p) {
     __shared__ EpilogueSmem sm;
+    grid_dependency_sync();
     const float static_scale = p.ep.q.mode == kQuantStatic ? *p.ep.scale_out : 1.f;
     int parity = 0;
     for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
@@ -101,6 +105,7 @@ __global__ void __launch_bounds__(tile_max_threads<VPT>(), staged_min_blocks<VPT
     extern __shared__ __align__(128) unsigned char stage_mem[];
     __shared__ EpilogueSmem sm;
     __shared__ __align__(8) uint64_t full[STAGES];
+    grid_dependency_sync();
     const uint32_t row_bytes = static_cast<uint32_t>(p.ep.row_vecs) * 16u;
     const int64_t nk = blockIdx.x < p.rows ? (p.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     auto issue = [&](int64_t k) {
@@ -164,6 +169,12 @@ struct ArParams {
     int64_t os_slot_bytes;   // one-shot: stride between slots; a buffer is N slots
     int roles;               // two-shot: 1 = every CTA runs all three stages of its chunks,
                              // 3 = CTAs specialise (3*lane + {0: scatter, 1: reduce+gather, 2: epilogue})
+    // exchange through symmetric memory (ar_sym_kernel): the same layout in every rank's buffer
+    char *sym[kMaxRanks];    // every rank's symmetric buffer as mapped here ([rank] is local)
+    char *sym_mc;            // NVSwitch multicast mapping of those buffers (nullptr: none)
+    int64_t sym_in_off;      // copy of the rank's input, laid out like the input
+    int64_t sym_out_off;     // the reduced tensor, laid out like the input
+    int64_t sym_flag_off;    // uint64 flags[2][kMaxBlocks][kMaxRanks], written by the rank of the last index
 };
 
 __device__ __forceinline__ int row_len(const ArParams &p, int row) {
@@ -326,7 +337,7 @@ __device__ __noinline__ void finish_rows(const ArParams &p, int64_t ts, int r0, 
 // ---- the body: one CTA of one rank ------------------------------------------------------
 
 // Takes this CTA's ticket of the call and learns the call's number from the same atomic:
-// LocalState::seq holds the number of completed exchanges in its upper 16 bits (the low bit
+// LocalState::seq holds the number of completed exchanges in its upper 48 bits (the low bit
 // of that number selects the staging buffer of this call) and the tickets taken so far by
 // CTAs of the running call in its lower 16 bits.  The CTA that takes the last ticket clears
 // the tickets and advances the number; every CTA of the call has read it by then, so the new
@@ -334,9 +345,9 @@ __device__ __noinline__ void finish_rows(const ArParams &p, int64_t ts, int r0, 
 // `sm.seq`; the caller passes a block barrier before reading it.
 __device__ __forceinline__ void begin_call(LocalState *st, int nb, EpilogueSmem &sm) {
     if (threadIdx.x == 0) {
-        const uint32_t old = atomicAdd(&st->seq, 1u);
+        const unsigned long long old = atomicAdd(&st->seq, 1ull);
         sm.seq = old >> 16;
-        if ((old & 0xffffu) == static_cast<uint32_t>(nb) - 1u) atomicAdd(&st->seq, 0x10000u - static_cast<uint32_t>(nb));
+        if ((old & 0xffffull) == static_cast<unsigned long long>(nb) - 1ull) atomicAdd(&st->seq, 0x10000ull - static_cast<unsigned long long>(nb));
     }
 }
 
@@ -354,7 +365,7 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
     if constexpr (TWO_SHOT) {
         begin_call(st, nb, sm);
         __syncthreads();
-        const int64_t ts = static_cast<int64_t>(sm.seq & 1u) * p.ts_stride;
+        const int64_t ts = static_cast<int64_t>(sm.seq & 1ull) * p.ts_stride;
         if (p.roles == 3) {
             // Specialised roles: the three stages of a lane's chunks run in three CTAs that meet
             // only through the staging memory.
@@ -414,7 +425,7 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
                 // the counter is fetched while the first row's loads are in flight
                 begin_call(st, nb, sm);
                 __syncthreads();
-                bo = p.os_off + static_cast<int64_t>(sm.seq & 1u) * NR * p.os_slot_bytes;
+                bo = p.os_off + static_cast<int64_t>(sm.seq & 1ull) * NR * p.os_slot_bytes;
             }
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -464,10 +475,190 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// N GPUs, bandwidth regime, through symmetric memory and the NVSwitch
+// ---------------------------------------------------------------------------------------
+// Every rank owns a buffer with the same layout (input copy | reduced tensor | flags), mapped
+// by all ranks and, with MC, also behind one multicast address.  For a chunk of rows, CTA b of
+// every rank
+//   1. copies its rows of the rank's input into its own buffer and raises flag[0][b][rank] on
+//      all ranks;
+//   2. once all N flags of the chunk are up, reduces the column slice this rank owns: with MC
+//      one multimem load per 16 bytes returns the sum over all ranks, added in the switch, and
+//      one multimem store writes it to every rank's reduced tensor; without MC the slice is
+//      read from every rank's buffer, summed in rank order and stored rank by rank.  Then
+//      raises flag[1][b][rank] on all ranks;
+//   3. once all N of those are up, runs the epilogue on whole rows of its own reduced tensor.
+// With MC a GPU sends and receives S(1 + 1/N) bytes per direction for a message of S bytes,
+// where the push exchange moves 2S(N-1)/N: 1.56x less at N = 8.
+// Flags carry (call number << 20 | chunk + 1) and only grow, so nothing is ever reset, and the
+// buffers need no double buffering: a rank's kernel ends only after every peer has raised the
+// stage-2 flags of all chunks, i.e. after every peer has finished reading this rank's input
+// copy; and a peer's stage-2 stores of the next call wait for this rank's stage-1 flag of the
+// next call.  The three steps of consecutive chunks are staggered as in the push exchange.
+constexpr int kSymFlagStages = 2;
+constexpr int64_t kSymFlagBytes = static_cast<int64_t>(kSymFlagStages) * kMaxBlocks * kMaxRanks * 8;
+
+template <typename T>
+__device__ __noinline__ void sym_stage_in(const ArParams &p, int r0, int r1) {
+    constexpr int U = 4;
+    const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
+    uint4 *dst = reinterpret_cast<uint4 *>(p.sym[p.rank] + p.sym_in_off);
+    const int64_t v_begin = static_cast<int64_t>(r0) * p.row_vecs, v_end = static_cast<int64_t>(r1) * p.row_vecs;
+    const int B = blockDim.x;
+    for (int64_t v0 = v_begin + threadIdx.x; v0 < v_end; v0 += U * B) {
+        uint4 val[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (v0 + u * B < v_end) val[u] = ld_stream(in + v0 + u * B);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (v0 + u * B < v_end) st_peer(dst + v0 + u * B, val[u]);
+    }
+}
+
+template <typename T, int NR, bool MC>
+__device__ __noinline__ void sym_reduce_bcast(const ArParams &p, int r0, int r1) {
+    constexpr int IB = MC ? 4 : (NR >= 8 ? 1 : (NR == 4 ? 2 : 4));
+    const int items = (r1 - r0) * p.vpr;
+    const int B = blockDim.x;
+    for (int it0 = threadIdx.x; it0 < items; it0 += IB * B) {
+        int64_t off[IB];
+        uint4 red[IB];
+        uint4 part[MC ? 1 : IB][MC ? 1 : NR];
+#pragma unroll
+        for (int b = 0; b < IB; ++b) {
+            const int it = it0 + b * B;
+            off[b] = -1;
+            if (it < items) {
+                const int rr = it / p.vpr;
+                const int v = p.rank * p.vpr + (it - rr * p.vpr);
+                if (v < p.row_vecs) {
+                    off[b] = (static_cast<int64_t>(r0 + rr) * p.row_vecs + v) * 16;
+                    if constexpr (MC) {
+                        red[b] = multimem_ld_sum<T>(p.sym_mc + p.sym_in_off + off[b]);
+                    } else {
+#pragma unroll
+                        for (int s = 0; s < NR; ++s) part[b][s] = ld_poll(p.sym[s] + p.sym_in_off + off[b]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < IB; ++b) {
+            if (off[b] >= 0) {
+                if constexpr (MC) {
+                    multimem_st(p.sym_mc + p.sym_out_off + off[b], red[b]);
+                } else {
+                    const uint4 r = sum_in_rank_order<T, NR>(part[b]);
+#pragma unroll
+                    for (int d = 0; d < NR; ++d) st_peer(p.sym[(p.rank + d) % NR] + p.sym_out_off + off[b], r);
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int VPT>
+__device__ __noinline__ void sym_finish_rows(const ArParams &p, int r0, int r1, EpilogueSmem &sm, int &parity, float static_scale) {
+    const uint4 *out = reinterpret_cast<const uint4 *>(p.sym[p.rank] + p.sym_out_off);
+    const RowSeg seg = whole_row(p.row_vecs);
+    for (int row = r0; row < r1; ++row) {
+        const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
+        uint4 x[VPT], res[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * blockDim.x;
+            x[i] = v < p.row_vecs ? ld_staging(out + base + v) : make_uint4(0, 0, 0, 0);
+        }
+        load_residual<T, VPT>(p.ep, seg, row, res);
+        row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
+        parity ^= 1;
+    }
+}
+
+template <typename T, int NR, int VPT, bool MC>
+__device__ __forceinline__ void ar_sym_body(const ArParams &p, int vb, int nb, EpilogueSmem &sm) {
+    LocalState *st = p.st;
+    const float static_scale = p.ep.q.mode == kQuantStatic ? *p.ep.scale_out : 1.f;
+    begin_call(st, nb, sm);
+    __syncthreads();
+    const unsigned long long call = sm.seq;
+    const int R = p.rows_per_chunk;
+    const int nchunks = (p.rows + R - 1) / R;
+    const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;
+    auto r0_of = [&](int k) { return (vb + k * nb) * R; };
+    auto r1_of = [&](int k) { const int r1 = (vb + k * nb) * R + R; return r1 < p.rows ? r1 : p.rows; };
+    auto flag_index = [&](int stage, int src) { return (static_cast<int64_t>(stage) * kMaxBlocks + vb) * kMaxRanks + src; };
+    auto tag = [&](int k) { return (call << 20) | static_cast<unsigned long long>(k + 1); };
+    // publish: everything this CTA has written so far is visible to a rank that sees the flag
+    auto raise = [&](int stage, int k) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            const int64_t idx = flag_index(stage, p.rank);
+            if constexpr (MC) {
+                multimem_st_flag_release(reinterpret_cast<unsigned long long *>(p.sym_mc + p.sym_flag_off) + idx, tag(k));
+            } else {
+#pragma unroll
+                for (int j = 0; j < NR; ++j)
+                    st_flag_release(reinterpret_cast<unsigned long long *>(p.sym[j] + p.sym_flag_off) + idx, tag(k));
+            }
+        }
+    };
+    auto await = [&](int stage, int k) {
+        if (threadIdx.x < NR)
+            wait_flag(reinterpret_cast<const unsigned long long *>(p.sym[p.rank] + p.sym_flag_off) + flag_index(stage, threadIdx.x),
+                      tag(k), st, p.rank, stage == 0 ? kStageSymIn : kStageSymOut, threadIdx.x);
+        __syncthreads();
+    };
+    int parity = 0;
+    const int steps = nk > 0 ? nk + 2 : 0;
+    for (int s = 0; s < steps; ++s) {
+        if (s < nk) {
+            sym_stage_in<T>(p, r0_of(s), r1_of(s));
+            raise(0, s);
+        }
+        const int kr = s - 1;
+        if (kr >= 0 && kr < nk) {
+            await(0, kr);
+            sym_reduce_bcast<T, NR, MC>(p, r0_of(kr), r1_of(kr));
+            raise(1, kr);
+        }
+        const int kf = s - 2;
+        if (kf >= 0 && kf < nk) {
+            await(1, kf);
+            sym_finish_rows<T, VPT>(p, r0_of(kf), r1_of(kf), sm, parity, static_scale);
+        }
+    }
+}
+
+template <typename T, int NR, int VPT, bool MC>
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), ar_min_blocks<VPT>())
+    ar_sym_kernel(const __grid_constant__ ArParams p) {
+    __shared__ EpilogueSmem sm;
+    grid_dependency_sync();
+    ar_sym_body<T, NR, VPT, MC>(p, blockIdx.x, gridDim.x, sm);
+}
+
+// The same for N ranks inside one launch on one GPU (peer loads instead of the multicast).
+template <typename T, int NR, int VPT>
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), ar_min_blocks<VPT>())
+    ar_sym_emulated_kernel(const ArParams *params_by_rank, int nb) {
+    __shared__ EpilogueSmem sm;
+    __shared__ ArParams p;
+    const int rank = blockIdx.x / nb;
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(ArParams) / 4); i += blockDim.x)
+        reinterpret_cast<uint32_t *>(&p)[i] = reinterpret_cast<const uint32_t *>(params_by_rank + rank)[i];
+    __syncthreads();
+    ar_sym_body<T, NR, VPT, false>(p, blockIdx.x % nb, nb, sm);
+}
+
 template <typename T, int NR, int VPT, bool TWO_SHOT, bool FUSED>
 __global__ void __launch_bounds__(tile_max_threads<VPT>(), ar_min_blocks<VPT>())
     ar_kernel(const __grid_constant__ ArParams p) {
     __shared__ EpilogueSmem sm;
+    grid_dependency_sync();
     ar_body<T, NR, VPT, TWO_SHOT, FUSED>(p, blockIdx.x, gridDim.x, sm);
 }
 

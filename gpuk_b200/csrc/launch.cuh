@@ -15,11 +15,17 @@ struct ArShape {
     int threads;
     int grid;        // CTAs per rank (a multiple of `cluster`)
     int cluster;     // CTAs per thread-block cluster (1: launched without a cluster attribute)
+    int sym;         // 0: push exchange; 1: exchange through symmetric memory with peer loads;
+                     // 2: the same with NVSwitch multicast (two_shot is true for 1 and 2)
 };
 
 // Launches `fn` (one parameter block behind args) with an optional cluster dimension; with
 // `all_resident` the launch is cooperative, i.e. refused unless the whole grid fits the GPU.
-cudaError_t launch_kernel(const void *fn, int grid, int threads, int cluster, bool all_resident, void **args, cudaStream_t stream);
+// Other launches are programmatic dependent launches (unless GPUK_PDL=0): the kernels wait
+// for the preceding grid themselves (griddepcontrol.wait) before they touch memory, so their
+// CTAs may be placed on the SMs while the tail of the preceding kernel is still running.
+cudaError_t launch_kernel(const void *fn, int grid, int threads, int cluster, bool all_resident, void **args, cudaStream_t stream,
+                          size_t dynamic_smem = 0);
 // CTAs of `fn` that can be resident on the whole GPU at once, counting whole clusters only.
 cudaError_t resident_ctas(const void *fn, int threads, int cluster, int sm_count, int64_t *ctas);
 

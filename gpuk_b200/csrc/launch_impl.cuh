@@ -15,7 +15,16 @@ static const void *ar_fn(bool emulated) {
 }
 
 template <typename T, int NR, int VPT>
+static const void *ar_sym_fn(const ArShape &s, bool emulated) {
+    if (!s.fused) return nullptr;   // the plain all-reduce uses the push exchange
+    if (emulated) return s.sym == 1 ? reinterpret_cast<const void *>(&ar_sym_emulated_kernel<T, NR, VPT>) : nullptr;
+    return s.sym == 2 ? reinterpret_cast<const void *>(&ar_sym_kernel<T, NR, VPT, true>)
+                      : reinterpret_cast<const void *>(&ar_sym_kernel<T, NR, VPT, false>);
+}
+
+template <typename T, int NR, int VPT>
 static const void *ar_fn_modes(const ArShape &s, bool emulated) {
+    if (s.sym) return ar_sym_fn<T, NR, VPT>(s, emulated);
     if (s.fused) return s.two_shot ? ar_fn<T, NR, VPT, true, true>(emulated) : ar_fn<T, NR, VPT, false, true>(emulated);
     if constexpr (VPT == 4) {   // the plain all-reduce is only built for the 4-vector tile
         return s.two_shot ? ar_fn<T, NR, VPT, true, false>(emulated) : ar_fn<T, NR, VPT, false, false>(emulated);
@@ -55,7 +64,7 @@ cudaError_t launch_norm_quant(const NormQuantParams &p, int vpt, int threads, in
     default: return cudaErrorInvalidValue;
     }
     void *args[] = {const_cast<NormQuantParams *>(&p)};
-    return cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, 0, stream);
+    return launch_kernel(fn, grid, threads, 1, false, args, stream);
 }
 
 template <typename T, int VPT, int STAGES>
@@ -83,7 +92,7 @@ static cudaError_t launch_staged_one(const NormQuantParams &p, int threads, int 
     const int64_t slots = static_cast<int64_t>(per_sm_by_device[device]) * sm_count;
     const int grid = static_cast<int>(p.rows < slots ? p.rows : slots);
     void *args[] = {const_cast<NormQuantParams *>(&p)};
-    return cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, smem, stream);
+    return launch_kernel(fn, grid, threads, 1, false, args, stream, smem);
 }
 
 template <typename T>

@@ -75,7 +75,6 @@ __global__ void scratch_init_kernel(unsigned char *base, unsigned long long time
     if (blockIdx.x == 0 && threadIdx.x < kMaxRanks) {
         LocalState *st = reinterpret_cast<LocalState *>(base + threadIdx.x * 256);
         st->seq = 0;
-        st->reserved = 0;
         st->reserved2 = 0;
         st->abort = 0;
         st->timeout_ns = timeout_ns;

@@ -104,6 +104,25 @@ int gpuk_ws_open_data_handles(gpuk_ws *ws, const uint8_t *handles, int n);
  */
 int gpuk_ws_local_pointers(gpuk_ws *ws, void **flags, void **data);
 int gpuk_ws_set_peer_pointers(gpuk_ws *ws, void *const *flags, void *const *data, int n);
+/*
+ * Optional second exchange for the bandwidth regime, through symmetric memory: `bases[r]` is
+ * rank r's buffer of `bytes` bytes as mapped in this process (same size on every rank, 256-byte
+ * aligned; bases[rank] is this rank's own) and `mc_base` the NVSwitch multicast mapping of the
+ * same buffers, or NULL.  The caller allocates and maps them (for one process per GPU e.g. with
+ * torch.distributed._symmetric_memory, which is how GPUKDistEnv does it) and keeps them alive
+ * while the workspace exists; the last 256 KiB hold flags and must be zero on every rank before
+ * the first call.  With a multicast mapping the reduction runs inside the switch
+ * (multimem.ld_reduce) and a GPU moves S(1 + 1/N) bytes per direction instead of 2S(N-1)/N;
+ * the switch rounds the 16-bit sum in its own way (measured on B200: ties away from zero, so
+ * about 15 % of the sums differ from round-to-nearest-even by one unit in the last place),
+ * which is outside this library's parity bars: option "sym_multicast" = 0 keeps the exchange
+ * but reads the peers' buffers with plain loads and sums in rank order, bit-exact.
+ * Fused calls whose message is at least the option "sym_min_bytes" (default: never) and fits
+ * (bytes - 256 KiB) / 2 take this exchange.  The reference has no counterpart (it pulls from
+ * IPC-registered inputs, all_reduce_fusion.cpp:105-137).
+ */
+int gpuk_ws_attach_symmetric(gpuk_ws *ws, void *const *bases, int n, void *mc_base, int64_t bytes);
+
 /* Replaces enable_p2p (src/common/communicator.h:40-55): peer access among devices 0..n-1. */
 int gpuk_enable_peer_access(int n_devices);
 
@@ -190,6 +209,12 @@ typedef struct gpuk_plan {
     int lead_push;      /* two-shot pipeline: chunks the scatter runs ahead of the reduction */
     int lead_reduce;    /* two-shot pipeline: chunks the reduction runs ahead of the epilogue */
 } gpuk_plan;
+
+/* force_mode values of gpuk_emulated_allreduce_rms */
+#define GPUK_MODE_AUTO 0
+#define GPUK_MODE_ONE_SHOT 1
+#define GPUK_MODE_TWO_SHOT 2
+#define GPUK_MODE_SYMMETRIC 3   /* through symmetric memory (gpuk_ws_attach_symmetric) */
 
 /*
  * Launch plan for a message of `numel` elements in rows of `hidden` on `world_size` ranks.

@@ -173,11 +173,12 @@ class ParityReport:
 
         The row maximum is a 16-bit value: when the two sides' fp32 row statistics differ in the
         last bit, that value can round to the neighbouring 16-bit number on one side, which moves
-        the scale by one 16-bit step (2^-8 .. 2^-7 relative).  Such a row is tolerated only as an
-        outlier: at most one row, or 0.1 % of the rows, and never by more than one step.
+        the scale by one 16-bit step (2^-8 .. 2^-7 relative); the multiplication by the weight
+        rounds once more and can carry that to a second step.  Such a row is tolerated only as an
+        outlier: at most one row, or 0.1 % of the rows, and never by more than two steps.
         """
         assert self.fp8_within_1ulp_frac >= fp8_frac, self
-        assert self.scale_max_rel <= scale_step, self
+        assert self.scale_max_rel <= 2 * scale_step, self
         assert self.scale_rows_beyond_1e3 <= max(1, self.scale_rows // 1000), self
         if self.scale_rows_beyond_1e3 == 0:
             assert self.scale_max_rel <= scale_rel, self

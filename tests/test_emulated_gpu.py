@@ -10,7 +10,7 @@ from oracle import epilogue_oracle as eo   # noqa: E402
 from gpuk_b200 import workloads as oin           # noqa: E402
 from tests import util                     # noqa: E402
 
-ONE_SHOT, TWO_SHOT = 1, 2
+ONE_SHOT, TWO_SHOT, SYMMETRIC = 1, 2, 3
 
 
 def _check_all_ranks(outs, want, quant):
@@ -146,6 +146,47 @@ def test_one_shot_rows_split_over_a_cluster(world, tokens, hidden, quant):
             outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=ONE_SHOT)
             want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
             _check_all_ranks(outs, want, quant)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("tokens,hidden,quant,rows_per_chunk", [
+    (1, 4096, 3, 0), (129, 1024, 1, 0), (700, 2048, 3, 3), (37, 7168, 4, 0), (1500, 1024, 0, 2), (5, 2056, 3, 0)])
+def test_exchange_through_symmetric_memory(world, tokens, hidden, quant, rows_per_chunk):
+    """Copy-in, flag, slice reduction from every rank's buffer, broadcast, flag, epilogue -- here
+    with peer loads standing in for the switch reduction; three calls in a row on the same buffers
+    (no double buffering: the flags alone keep consecutive calls apart)."""
+    static = 0.05 if quant == 4 else None
+    with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        g.attach_symmetric(tokens * hidden * 2)
+        if rows_per_chunk:
+            g.set_option("rows_per_chunk", rows_per_chunk)
+        for call in range(3):
+            parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 17 + tokens + call)
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=SYMMETRIC)
+            want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
+            _check_all_ranks(outs, want, quant)
+
+
+def test_symmetric_exchange_interleaved_with_the_push_exchange_and_refused_without_a_buffer():
+    from gpuk_b200 import cabi
+    world = 4
+    parts, res, w = util.random_case(world, 300, 2048, torch.bfloat16, seed=77)
+    d = [p.cuda() for p in parts], res.cuda(), w.cuda()
+    want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
+    with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        with pytest.raises(cabi.GpukError) as e:
+            g.fused(*d, 1e-6, 3, force_mode=SYMMETRIC)
+        assert e.value.status == cabi.ERR_NOT_READY
+        g.attach_symmetric(300 * 2048 * 2)
+        for mode in (SYMMETRIC, TWO_SHOT, SYMMETRIC, ONE_SHOT, SYMMETRIC):
+            _check_all_ranks(g.fused(*d, 1e-6, 3, force_mode=mode), want, 3)
+        # automatic choice by message size
+        g.set_option("sym_min_bytes", 1 << 20)
+        _check_all_ranks(g.fused(*d, 1e-6, 3), want, 3)
+        big, res2, w2 = util.random_case(world, 301, 2048, torch.bfloat16, seed=78)
+        with pytest.raises(cabi.GpukError) as e:
+            g.fused([p.cuda() for p in big], res2.cuda(), w2.cuda(), 1e-6, 3, force_mode=SYMMETRIC)
+        assert e.value.status == cabi.ERR_TOO_LARGE
 
 
 def test_benchmark_decode_config_eight_ranks():

@@ -52,6 +52,18 @@ class PeerGroup:
         for h in self.ws:
             self.cabi.lib.gpuk_ws_destroy(h)
 
+    def attach_symmetric(self, message_bytes, min_bytes):
+        """Plain device buffers with peer access stand in for symmetric memory (no multicast mapping)."""
+        cabi = self.cabi
+        nbytes = (2 * ((message_bytes + 255) // 256 * 256) + cabi.SYM_FLAG_BYTES + 1023) // 256 * 256
+        self.sym = [torch.zeros(nbytes, dtype=torch.uint8, device=f"cuda:{r}") for r in range(self.world)]
+        for r in range(self.world):
+            torch.cuda.synchronize(r)
+        bases = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.sym])
+        for h in self.ws:
+            cabi.check(cabi.lib.gpuk_ws_attach_symmetric(h, bases, self.world, None, nbytes))
+            cabi.check(cabi.lib.gpuk_ws_set_option(h, b"sym_min_bytes", min_bytes))
+
     def fused(self, parts, residual, weight, eps, quant, static_scale=None):
         cabi = self.cabi
         dev = [(parts[r].cuda(r), residual.cuda(r), weight.cuda(r)) for r in range(self.world)]
@@ -90,6 +102,24 @@ def test_single_process_peer_access(world):
         g.close()
 
 
+@needs2
+@pytest.mark.parametrize("world", _worlds())
+def test_single_process_exchange_through_symmetric_memory(world):
+    """The pull variant (peer loads, rank-order sum) of the exchange through symmetric memory over real NVLink."""
+    g = PeerGroup(world)
+    try:
+        g.attach_symmetric(2048 * 7168 * 2, 1)
+        for i, (tokens, hidden, quant) in enumerate([(1024, 8192, 3), (129, 1024, 1), (2048, 7168, 3), (1024, 8192, 3), (37, 7168, 0)]):
+            parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 200 + i)
+            outs = g.fused(parts, res, w, 1e-6, quant)
+            want = eo.epilogue_t1(parts, res, w, 1e-6, quant)
+            for got in outs:
+                util.check_against_oracle(got, want, quant)
+                assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8))
+    finally:
+        g.close()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -106,13 +136,16 @@ def _ipc_worker(rank, world, port, cases, q):
                             device_id=torch.device("cuda", rank))
     import gpuk_b200
     from gpuk_b200 import cabi
-    env = gpuk_b200.GPUKDistEnv(group=None, device_id=rank, max_size_in_bytes=64 << 20)
+    env = gpuk_b200.GPUKDistEnv(group=None, device_id=rank, max_size_in_bytes=64 << 20, symmetric_bytes=40 << 20)
     failures = []
     try:
         for i, (tokens, hidden, fp8_out) in enumerate(cases):
             parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=900 + i)
             x = parts[rank].cuda()
             r_d, w_d = res.cuda(), w.cuda()
+            # large cases go through symmetric memory, read with plain peer loads (bit-exact)
+            env.set_option("sym_multicast", 0)
+            env.set_option("sym_min_bytes", 1 << 20 if i % 2 == 0 else 0)
             got = env.allreduce_add_rms_fused(x.clone(), r_d, w_d, 1e-6, fp8_out)
             nat = env.allreduce_add_rms_native(x.clone(), r_d, w_d, 1e-6, fp8_out)
             torch.cuda.synchronize()
@@ -128,6 +161,22 @@ def _ipc_worker(rank, world, port, cases, q):
                 assert torch.equal(plain.cpu().view(torch.int16), eo.allreduce_t1(parts).view(torch.int16))
             except AssertionError as e:   # pragma: no cover
                 failures.append(f"case {i} {tokens}x{hidden}: {e}")
+        if env.multicast:
+            # The same exchange reduced inside the NVSwitch.  The switch rounds 16-bit sums its own way
+            # (ties away from zero), so about one sum in seven is off by one unit in the last place:
+            # outside the parity bars, therefore opt-in, and checked here for closeness only.
+            env.set_option("sym_multicast", 1)
+            env.set_option("sym_min_bytes", 1)
+            parts, res, w = util.random_case(world, 700, 4096, torch.bfloat16, seed=4242)
+            got = env.allreduce_add_rms_fused(parts[rank].cuda(), res.cuda(), w.cuda(), 1e-6, False)
+            torch.cuda.synchronize()
+            want = eo.epilogue_t1(parts, res, w, 1e-6, 0)
+            try:
+                torch.testing.assert_close(got[0].cpu().float(), want[0].float(), atol=4e-2, rtol=2e-2)
+                torch.testing.assert_close(got[1].cpu().float(), want[1].float(), atol=4e-2, rtol=2e-2)
+            except AssertionError as e:   # pragma: no cover
+                failures.append(f"multicast: {e}")
+            env.set_option("sym_min_bytes", 0)
         out = (ctypes.c_uint32 * 8)()
         rc = cabi.lib.gpuk_ws_status(ctypes.c_void_p(env.fptr), out)
         if rc:
@@ -145,7 +194,8 @@ def test_one_process_per_gpu_over_ipc(world):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    cases = [(8, 8192, True), (1, 4096, True), (129, 1024, True), (1024, 8192, True), (8, 8192, False), (512, 7168, True)]
+    cases = [(8, 8192, True), (1, 4096, True), (1024, 8192, True), (1024, 8192, True), (1100, 7168, False), (512, 7168, True),
+             (901, 2056, True), (129, 1024, True)]
     port = _free_port()
     procs = [ctx.Process(target=_ipc_worker, args=(r, world, port, cases, q)) for r in range(world)]
     for p in procs:

@@ -76,6 +76,14 @@ class EmulatedGroup:
         for h in self.ws:
             cabi.check(cabi.lib.gpuk_ws_set_option(h, name.encode(), value))
 
+    def attach_symmetric(self, message_bytes: int):
+        """One zeroed buffer per emulated rank for the exchange through symmetric memory (no multicast)."""
+        nbytes = (2 * ((message_bytes + 255) // 256 * 256) + cabi.SYM_FLAG_BYTES + 1023) // 256 * 256
+        self.sym = [torch.zeros(nbytes, dtype=torch.uint8, device=f"cuda:{self.device}") for _ in range(self.world)]
+        bases = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.sym])
+        for h in self.ws:
+            cabi.check(cabi.lib.gpuk_ws_attach_symmetric(h, bases, self.world, None, nbytes))
+
     def __enter__(self):
         return self
 
