@@ -141,7 +141,6 @@ constexpr int64_t kRsSlack = 1 << 20;           // room for ceil(row_vecs / N) r
 constexpr uint64_t kDefaultTimeoutNs = 2000000000ull;
 constexpr size_t kFlagBytes = 4096;             // the allocation behind the "barrier handle"
 constexpr int64_t kTailBytes = 256;             // never written by an exchange
-constexpr int kDefaultRoles = 1;                // two-shot CTA organisation unless GPUK_ROLES says otherwise
 constexpr int kPlainRowVecs = 1024;             // the plain all-reduce views its input as 16 KiB rows
 constexpr int kDefaultK1Stages = 3;             // shared-memory stages of the one-GPU kernel for many rows (0: off)
 constexpr int kK1StagedMinRowsPerSm = 16;       // ... used from this many rows per SM (measured: 0.94 vs 0.89 of HBM peak
@@ -233,7 +232,7 @@ struct gpuk_ws {
     bool have_data = false, have_flags = false;
     std::vector<void *> ipc_opened;
     int64_t oneshot_max_bytes = 0;
-    int opt_roles = 0, opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default / environment
+    int opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default / environment
     int opt_lead_push = 0, opt_lead_reduce = 0;
     // exchange through symmetric memory (gpuk_ws_attach_symmetric)
     char *sym[kMaxRanks] = {};
@@ -306,7 +305,9 @@ int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype
     int vpt = 4, threads = 256;
     if (fused || one_shot) {
         // the row must fit one CTA's tile whichever exchange is chosen, clusters or not
-        if (!pick_tile(row_vecs, latency, &vpt, &threads) || !pick_tile(seg_vecs, latency, &vpt, &threads))
+        // (the two-shot kernels are built for the bandwidth tile only)
+        const bool wide = latency && (one_shot || world_size == 1);
+        if (!pick_tile(row_vecs, wide, &vpt, &threads) || !pick_tile(seg_vecs, wide, &vpt, &threads))
             return fail(GPUK_ERR_UNSUPPORTED, "row of %d vectors is longer than the largest tile", row_vecs);
         if (!fused) { vpt = 4; threads = std::max(32, ((row_vecs + 3) / 4 + 31) / 32 * 32); }
     }
@@ -579,10 +580,7 @@ int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes) {
 int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     if (!ws || !name) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace or option name");
     const std::string n(name);
-    if (n == "roles") {
-        if (value != 0 && value != 1 && value != 3) return fail(GPUK_ERR_INVALID_ARGUMENT, "roles must be 0, 1 or 3");
-        ws->opt_roles = static_cast<int>(value);
-    } else if (n == "rows_per_chunk") {
+    if (n == "rows_per_chunk") {
         if (value < 0 || value > 64) return fail(GPUK_ERR_INVALID_ARGUMENT, "rows_per_chunk must be in [0, 64]");
         ws->opt_rows_per_chunk = static_cast<int>(value);
     } else if (n == "ctas_per_sm") {
@@ -801,17 +799,6 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     }
     if (emulated) resident = resident / ws->world / plan.cluster * plan.cluster;
     const int64_t nchunks = (static_cast<int64_t>(plan.rows) + plan.rows_per_chunk - 1) / plan.rows_per_chunk;
-    static const int env_roles_ = [] { const char *e = getenv("GPUK_ROLES"); return e ? atoi(e) : 0; }();
-    const int env_roles = ws->opt_roles ? ws->opt_roles : env_roles_;
-    const int roles = (!one_shot && !sym && (env_roles == 3 || (env_roles == 0 && kDefaultRoles == 3)) && resident >= 3) ? 3 : 1;
-    p->roles = roles;
-    if (roles == 3) {
-        // lanes of three specialised CTAs; flag rows are indexed by lane
-        int64_t lanes = std::min<int64_t>(std::min<int64_t>(resident, kMaxBlocks) / 3, nchunks);
-        if (lanes < 1) lanes = 1;
-        shape->grid = static_cast<int>(lanes * 3);
-        return GPUK_OK;
-    }
     int64_t clusters = std::min<int64_t>(std::min<int64_t>(plan.grid, resident) / plan.cluster, nchunks);
     if (clusters < 1) return fail(GPUK_ERR_UNSUPPORTED, "the GPU cannot hold one cluster of %d CTAs of the selected kernel", plan.cluster);
     shape->grid = static_cast<int>(clusters * plan.cluster);

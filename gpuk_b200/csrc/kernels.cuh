@@ -35,8 +35,8 @@
 //              rounds once and writes the reduced slice into every rank's gather area
 //              (all-gather by push); each rank then runs the epilogue on whole rows.  CTA b
 //              on every rank works on the same rows (the structural idea of
-//              communicator.h:82-88), and a CTA staggers its chunks: scatter k+1, reduce k,
-//              epilogue k-1.
+//              communicator.h:82-88), and a CTA staggers its chunks -- scatter k+1, reduce k,
+//              epilogue k-1 -- with the loads of the three roles in flight together.
 //
 // Staging is double-buffered by call parity (a device-side counter that the kernel advances
 // itself, so a replayed CUDA graph stays in step): a rank can start call c+2 only after every peer has pushed its call c+1
@@ -58,6 +58,12 @@ template <int VPT>
 constexpr int tile_min_blocks() { return VPT == 4 ? 4 : 1; }      // one-GPU kernel: 64 registers
 template <int VPT>
 constexpr int ar_min_blocks() { return VPT == 4 ? 3 : 1; }        // exchange kernels hold N vectors per item
+// The two-shot exchange always runs on the bandwidth tile (at most 256 threads, 512 for the
+// longest rows) and keeps the loads of three pipeline roles in registers: 128 registers.
+template <int VPT, bool TWO_SHOT>
+constexpr int ar_max_threads() { return TWO_SHOT ? (VPT == 8 ? 512 : 256) : tile_max_threads<VPT>(); }
+template <int VPT, bool TWO_SHOT>
+constexpr int ar_resident_blocks() { return TWO_SHOT ? (VPT == 8 ? 1 : 2) : ar_min_blocks<VPT>(); }
 
 // ---------------------------------------------------------------------------------------
 // one GPU: residual add + RMSNorm + FP8, no communication
@@ -167,8 +173,6 @@ struct ArParams {
     int64_t ts_stride;       // two-shot: bytes between buffer 0 and buffer 1
     int64_t os_off;          // one-shot: offset of buffer 0
     int64_t os_slot_bytes;   // one-shot: stride between slots; a buffer is N slots
-    int roles;               // two-shot: 1 = every CTA runs all three stages of its chunks,
-                             // 3 = CTAs specialise (3*lane + {0: scatter, 1: reduce+gather, 2: epilogue})
     // exchange through symmetric memory (ar_sym_kernel): the same layout in every rank's buffer
     char *sym[kMaxRanks];    // every rank's symmetric buffer as mapped here ([rank] is local)
     char *sym_mc;            // NVSwitch multicast mapping of those buffers (nullptr: none)
@@ -197,138 +201,112 @@ __device__ __forceinline__ uint4 sum_in_rank_order(const uint4 (&part)[NR]) {
     return Elem<T>::pack(acc);
 }
 
-// ---- two-shot stages -------------------------------------------------------------------
-// `ts` is the byte offset of this call's two-shot buffer inside every rank's staging memory.
-
-// Stage 1 (scatter): push the slices of rows [r0, r1) of my partial to their owners.
-template <typename T, int NR>
-__device__ __noinline__ void push_slices(const ArParams &p, int64_t ts, int r0, int r1) {
-    constexpr int U = 4;
-    const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
-    const int B = blockDim.x;
-    for (int row = r0; row < r1; ++row) {
-        const int len = row_len(p, row);
-        const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
-        for (int v0 = threadIdx.x; v0 < len; v0 += U * B) {
-            uint4 val[U];
-            int owner[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int v = v0 + u * B;
-                owner[u] = v < len ? v / p.vpr : p.rank;     // my own slice is summed straight from `in`
-                if (owner[u] != p.rank) val[u] = ld_stream(in + base + v);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int v = v0 + u * B;
-                if (owner[u] != p.rank) {
-                    char *slot = p.peer_data[owner[u]] + ts + p.rank * p.rs_slot_bytes;
-                    st_peer(reinterpret_cast<uint4 *>(slot) + static_cast<int64_t>(row) * p.vpr + (v - owner[u] * p.vpr),
-                            payload<T>(val[u]));
-                }
-            }
-        }
-    }
-}
-
-// Stage 2 (reduce + gather): as the slices of rows [r0, r1) land in my slots, sum each vector
-// over all ranks in rank order, round once, and push the result into every rank's gather area.
-template <typename T, int NR>
-__device__ __noinline__ void reduce_and_gather(const ArParams &p, int64_t ts, int r0, int r1) {
-    constexpr int IB = NR >= 8 ? 1 : (NR == 4 ? 2 : 4);   // items per batch: ~8 loads in flight per thread
+// ---- one pipeline step with all of its loads in flight together ----------------------------
+// Scatter of row `row_a`, reduction of this rank's slice of row `row_b` and finish of row
+// `row_c` (a negative row: nothing to do in that role).  The three roles belong to three
+// different chunks of the CTA's pipeline and do not depend on one another, so their loads --
+// the row of the input, the N slot vectors, the gathered row and its residual -- are issued back
+// to back before anything is consumed: a step exposes one memory round trip instead of three.
+template <typename T, int NR, int VPT, bool FUSED>
+__device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int row_a, int row_b, int row_c,
+                                              EpilogueSmem &sm, int &parity, float static_scale) {
+    constexpr int IBB = (VPT + NR - 1) / NR;     // slice vectors per thread: vpr <= VPT * blockDim / NR
     const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
     char *mine = p.peer_data[p.rank] + ts;
-    const int items = (r1 - r0) * p.vpr;
+    uint4 *ag = reinterpret_cast<uint4 *>(mine + p.ag_off);
     const int B = blockDim.x;
-    for (int it0 = threadIdx.x; it0 < items; it0 += IB * B) {
-        uint4 part[IB][NR];
-        int64_t dst[IB], src[IB];
+    const int len_a = row_a >= 0 ? row_len(p, row_a) : 0;
+    const int len_b = row_b >= 0 ? row_len(p, row_b) : 0;
+    const int len_c = row_c >= 0 ? row_len(p, row_c) : 0;
+    const int64_t base_a = static_cast<int64_t>(row_a) * p.row_vecs;
+    const int64_t base_b = static_cast<int64_t>(row_b) * p.row_vecs;
+    const int64_t base_c = static_cast<int64_t>(row_c) * p.row_vecs;
+    const int64_t slot_b = static_cast<int64_t>(row_b) * p.vpr;
+
+    // ---- issue: scatter
+    uint4 a[VPT];
+    int owner[VPT];
 #pragma unroll
-        for (int b = 0; b < IB; ++b) {
-            const int it = it0 + b * B;
-            dst[b] = -1;
-            if (it < items) {
-                const int rr = it / p.vpr;
-                const int vl = it - rr * p.vpr;
-                const int row = r0 + rr;
-                const int v = p.rank * p.vpr + vl;
-                if (v < row_len(p, row)) {
-                    dst[b] = static_cast<int64_t>(row) * p.row_vecs + v;
-                    src[b] = static_cast<int64_t>(row) * p.vpr + vl;
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * B;
+        owner[i] = v < len_a ? v / p.vpr : p.rank;     // my own slice is summed straight from `in`
+        if (owner[i] != p.rank) a[i] = ld_stream(in + base_a + v);
+    }
+    // ---- issue: reduction
+    uint4 part[IBB][NR];
+    bool have[IBB];
 #pragma unroll
-                    for (int s = 0; s < NR; ++s) {
-                        part[b][s] = s == p.rank ? ld_stream(in + dst[b])
-                                                 : ld_poll(reinterpret_cast<const uint4 *>(mine + s * p.rs_slot_bytes) + src[b]);
-                    }
+    for (int b = 0; b < IBB; ++b) {
+        const int vl = threadIdx.x + b * B;
+        have[b] = vl < p.vpr && p.rank * p.vpr + vl < len_b;
+        if (have[b]) {
+#pragma unroll
+            for (int s2 = 0; s2 < NR; ++s2)
+                part[b][s2] = s2 == p.rank ? ld_stream(in + base_b + p.rank * p.vpr + vl)
+                                           : ld_poll(reinterpret_cast<const uint4 *>(mine + s2 * p.rs_slot_bytes) + slot_b + vl);
+        }
+    }
+    // ---- issue: finish
+    uint4 x[VPT], res[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * B;
+        x[i] = v < len_c ? ld_poll(ag + base_c + v) : make_uint4(0, 0, 0, 0);
+    }
+    const RowSeg seg = whole_row(p.row_vecs);
+    if constexpr (FUSED) {
+        if (row_c >= 0) load_residual<T, VPT>(p.ep, seg, row_c, res);
+    }
+
+    // ---- consume: scatter
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * B;
+        if (owner[i] != p.rank) {
+            char *slot = p.peer_data[owner[i]] + ts + p.rank * p.rs_slot_bytes;
+            st_peer(reinterpret_cast<uint4 *>(slot) + static_cast<int64_t>(row_a) * p.vpr + (v - owner[i] * p.vpr), payload<T>(a[i]));
+        }
+    }
+    // ---- consume: reduction, then gather by push
+#pragma unroll
+    for (int b = 0; b < IBB; ++b) {
+        if (have[b]) {
+            const int vl = threadIdx.x + b * B;
+#pragma unroll
+            for (int s2 = 0; s2 < NR; ++s2) {
+                if (s2 != p.rank) {
+                    uint4 *addr = reinterpret_cast<uint4 *>(mine + s2 * p.rs_slot_bytes) + slot_b + vl;
+                    part[b][s2] = wait_landed(addr, part[b][s2], p.st, p.rank, kStageScatter, s2);
+                    st_empty(addr);
                 }
             }
-        }
+            const uint4 red = payload<T>(sum_in_rank_order<T, NR>(part[b]));
+            const int64_t dst = base_b + p.rank * p.vpr + vl;
 #pragma unroll
-        for (int b = 0; b < IB; ++b) {
-            if (dst[b] >= 0) {
-#pragma unroll
-                for (int s = 0; s < NR; ++s) {
-                    if (s != p.rank) {
-                        uint4 *addr = reinterpret_cast<uint4 *>(mine + s * p.rs_slot_bytes) + src[b];
-                        part[b][s] = wait_landed(addr, part[b][s], p.st, p.rank, kStageScatter, s);
-                        st_empty(addr);
-                    }
-                }
-                const uint4 red = payload<T>(sum_in_rank_order<T, NR>(part[b]));
-#pragma unroll
-                for (int d = 0; d < NR; ++d) {
-                    const int j = (p.rank + d) % NR;   // start with myself, then fan out: spreads the links
-                    st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + ts + p.ag_off) + dst[b], red);
-                }
+            for (int d = 0; d < NR; ++d) {
+                const int j = (p.rank + d) % NR;   // start with myself, then fan out: spreads the links
+                st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + ts + p.ag_off) + dst, red);
             }
         }
     }
-}
-
-// Stage 3: rows [r0, r1) arrive in my gather area, slice by slice from their owners.
-template <typename T, int NR, int VPT, bool FUSED>
-__device__ __noinline__ void finish_rows(const ArParams &p, int64_t ts, int r0, int r1, EpilogueSmem &sm, int &parity,
-                                            float static_scale) {
-    uint4 *ag = reinterpret_cast<uint4 *>(p.peer_data[p.rank] + ts + p.ag_off);
-    for (int row = r0; row < r1; ++row) {
-        const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
+    // ---- consume: finish
+    if (row_c >= 0) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * B;
+            if (v < len_c) {
+                x[i] = wait_landed(ag + base_c + v, x[i], p.st, p.rank, kStageGather, v / p.vpr);
+                st_empty(ag + base_c + v);
+            }
+        }
         if constexpr (FUSED) {
-            uint4 x[VPT], res[VPT];
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * blockDim.x;
-                x[i] = v < p.row_vecs ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
-            }
-            const RowSeg seg = whole_row(p.row_vecs);
-            load_residual<T, VPT>(p.ep, seg, row, res);
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * blockDim.x;
-                if (v < p.row_vecs) {
-                    x[i] = wait_landed(ag + base + v, x[i], p.st, p.rank, kStageGather, v / p.vpr);
-                    st_empty(ag + base + v);
-                }
-            }
-            row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
+            row_epilogue<T, VPT>(p.ep, seg, row_c, x, res, sm, parity, static_scale);
             parity ^= 1;
         } else {
-            constexpr int U = 4;
-            const int len = row_len(p, row);
-            const int B = blockDim.x;
-            for (int v0 = threadIdx.x; v0 < len; v0 += U * B) {
-                uint4 val[U];
 #pragma unroll
-                for (int u = 0; u < U; ++u)
-                    if (v0 + u * B < len) val[u] = ld_poll(ag + base + v0 + u * B);
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int v = v0 + u * B;
-                    if (v < len) {
-                        val[u] = wait_landed(ag + base + v, val[u], p.st, p.rank, kStageGather, v / p.vpr);
-                        st_empty(ag + base + v);
-                        st_stream(reinterpret_cast<uint4 *>(p.out) + base + v, val[u]);
-                    }
-                }
+            for (int i = 0; i < VPT; ++i) {
+                const int v = threadIdx.x + i * B;
+                if (v < len_c) st_stream(reinterpret_cast<uint4 *>(p.out) + base_c + v, x[i]);
             }
         }
     }
@@ -366,36 +344,26 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
         begin_call(st, nb, sm);
         __syncthreads();
         const int64_t ts = static_cast<int64_t>(sm.seq & 1ull) * p.ts_stride;
-        if (p.roles == 3) {
-            // Specialised roles: the three stages of a lane's chunks run in three CTAs that meet
-            // only through the staging memory.
-            const int lanes = nb / 3, lane = vb / 3, role = vb - lane * 3;
-            const int nl = lane < nchunks ? (nchunks - lane + lanes - 1) / lanes : 0;
-            for (int k = 0; k < nl; ++k) {
-                const int r0 = (lane + k * lanes) * R;
-                const int r1 = r0 + R < p.rows ? r0 + R : p.rows;
-                if (role == 0) push_slices<T, NR>(p, ts, r0, r1);
-                else if (role == 1) reduce_and_gather<T, NR>(p, ts, r0, r1);
-                else finish_rows<T, NR, VPT, FUSED>(p, ts, r0, r1, sm, parity, static_scale);
-            }
-        } else {
-            // Every CTA takes its chunks (vb, vb + nb, ...) through all three stages as a software
-            // pipeline: in step s it scatters chunk s, reduces chunk s - lead_push and finishes
-            // chunk s - lead_push - lead_reduce, so that traffic for later chunks is on the wire
-            // while the epilogue of an earlier one runs.  No stage waits for anything but its own
-            // input vectors.
-            const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;
-            auto r0_of = [&](int k) { return (vb + k * nb) * R; };
-            auto r1_of = [&](int k) { const int r1 = (vb + k * nb) * R + R; return r1 < p.rows ? r1 : p.rows; };
-            // a lead beyond the CTA's own chunks means "finish the earlier stage first"
-            const int lp = p.lead_push < nk ? p.lead_push : nk, lr = p.lead_reduce < nk ? p.lead_reduce : nk;
-            const int steps = nk > 0 ? nk + lp + lr : 0;
-            for (int s = 0; s < steps; ++s) {
-                if (s < nk) push_slices<T, NR>(p, ts, r0_of(s), r1_of(s));
-                const int kr = s - lp;
-                if (kr >= 0 && kr < nk) reduce_and_gather<T, NR>(p, ts, r0_of(kr), r1_of(kr));
-                const int kf = kr - lr;
-                if (kf >= 0 && kf < nk) finish_rows<T, NR, VPT, FUSED>(p, ts, r0_of(kf), r1_of(kf), sm, parity, static_scale);
+        // Every CTA takes its chunks (vb, vb + nb, ...) through the three roles as a software
+        // pipeline: in step s it scatters chunk s, reduces chunk s - lead_push and finishes chunk
+        // s - lead_push - lead_reduce, row by row, so that traffic for later chunks is on the wire
+        // while the epilogue of an earlier one runs.  Nothing waits for anything but its own input
+        // vectors.
+        const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;
+        auto r0_of = [&](int k) { return (vb + k * nb) * R; };
+        auto r1_of = [&](int k) { const int r1 = (vb + k * nb) * R + R; return r1 < p.rows ? r1 : p.rows; };
+        // a lead beyond the CTA's own chunks means "finish the earlier role first"
+        const int lp = p.lead_push < nk ? p.lead_push : nk, lr = p.lead_reduce < nk ? p.lead_reduce : nk;
+        const int steps = nk > 0 ? nk + lp + lr : 0;
+        for (int s = 0; s < steps; ++s) {
+            const int kr = s - lp, kf = kr - lr;
+            const bool do_a = s < nk, do_b = kr >= 0 && kr < nk, do_c = kf >= 0 && kf < nk;
+            for (int rr = 0; rr < R; ++rr) {
+                const int ra = do_a && r0_of(s) + rr < r1_of(s) ? r0_of(s) + rr : -1;
+                const int rb = do_b && r0_of(kr) + rr < r1_of(kr) ? r0_of(kr) + rr : -1;
+                const int rc = do_c && r0_of(kf) + rr < r1_of(kf) ? r0_of(kf) + rr : -1;
+                if (ra >= 0 || rb >= 0 || rc >= 0)
+                    two_shot_step<T, NR, VPT, FUSED>(p, ts, ra, rb, rc, sm, parity, static_scale);
             }
         }
     } else {
@@ -655,7 +623,7 @@ __global__ void __launch_bounds__(tile_max_threads<VPT>(), ar_min_blocks<VPT>())
 }
 
 template <typename T, int NR, int VPT, bool TWO_SHOT, bool FUSED>
-__global__ void __launch_bounds__(tile_max_threads<VPT>(), ar_min_blocks<VPT>())
+__global__ void __launch_bounds__(ar_max_threads<VPT, TWO_SHOT>(), ar_resident_blocks<VPT, TWO_SHOT>())
     ar_kernel(const __grid_constant__ ArParams p) {
     __shared__ EpilogueSmem sm;
     grid_dependency_sync();
@@ -665,7 +633,7 @@ __global__ void __launch_bounds__(tile_max_threads<VPT>(), ar_min_blocks<VPT>())
 // N ranks in one cooperative launch on one GPU: block b plays CTA (b % nb) of rank (b / nb).
 // All blocks are co-resident (cooperative launch), so the flag waits between "ranks" are safe.
 template <typename T, int NR, int VPT, bool TWO_SHOT, bool FUSED>
-__global__ void __launch_bounds__(tile_max_threads<VPT>(), ar_min_blocks<VPT>())
+__global__ void __launch_bounds__(ar_max_threads<VPT, TWO_SHOT>(), ar_resident_blocks<VPT, TWO_SHOT>())
     ar_emulated_kernel(const ArParams *params_by_rank, int nb) {
     __shared__ EpilogueSmem sm;
     __shared__ ArParams p;

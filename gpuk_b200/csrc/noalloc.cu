@@ -59,7 +59,7 @@ struct EmulatedParams {
 };
 
 template <typename T, int NR, int VPT, bool TWO_SHOT>
-__global__ void __launch_bounds__(tile_max_threads<VPT>(), 1)
+__global__ void __launch_bounds__(ar_max_threads<VPT, TWO_SHOT>(), 1)
     ar_selfcheck_kernel(const __grid_constant__ EmulatedParams ep, int nb) {
     __shared__ EpilogueSmem sm;
     const int rank = blockIdx.x / nb;
@@ -96,6 +96,8 @@ const void *kernel_for(int vpt, bool two_shot) {
                                   : reinterpret_cast<const void *>(&ar_selfcheck_kernel<T, NR, 1, false>);
     if (vpt == 2) return two_shot ? reinterpret_cast<const void *>(&ar_selfcheck_kernel<T, NR, 2, true>)
                                   : reinterpret_cast<const void *>(&ar_selfcheck_kernel<T, NR, 2, false>);
+    if (vpt == 4) return two_shot ? reinterpret_cast<const void *>(&ar_selfcheck_kernel<T, NR, 4, true>)
+                                  : reinterpret_cast<const void *>(&ar_selfcheck_kernel<T, NR, 4, false>);
     return nullptr;
 }
 
@@ -155,7 +157,7 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
                               "selfcheck: message of %lld bytes per rank exceeds the built-in scratch (limit %lld bytes); "
                               "use gpuk_emulated_allreduce_rms with workspaces for larger cases",
                               (long long)plan.message_bytes, (long long)kStaticMaxMessageBytes);
-    if (plan.vpt > 2)
+    if (plan.vpt > 4)
         return set_last_error(GPUK_ERR_UNSUPPORTED, "selfcheck: rows of %d vectors are not built for the no-allocation variant", plan.row_vecs);
     const bool two_shot = plan.one_shot == 0;
 
@@ -248,7 +250,6 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
         p.ts_stride = kTsStride;
         p.os_off = kOsOff;
         p.os_slot_bytes = kSlotBytes;
-        p.roles = 1;
     }
 
     scratch_clear_status_kernel<<<1, 32, 0, s>>>(base, world_size);

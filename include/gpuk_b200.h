@@ -228,10 +228,12 @@ int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype
 /* Override the crossover (bytes of one rank's input; <= 0 restores the default). */
 int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes);
 /*
- * Tuning options of the two-shot exchange; all ranks must set the same values.  Names:
- * "roles" (1: every CTA runs all stages of its chunks, 3: CTAs specialise into push / reduce /
- * epilogue, 0: default), "rows_per_chunk" (rows between two flag exchanges, 0: default),
- * "ctas_per_sm" (cap on resident CTAs per SM, 0: default), "oneshot_max_bytes".
+ * Tuning options of the exchanges; all ranks must set the same values.  Names:
+ * "rows_per_chunk" (rows a CTA takes through one pipeline role at a time, 0: default),
+ * "ctas_per_sm" (cap on resident CTAs per SM, 0: default), "lead_push" / "lead_reduce" (pipeline
+ * depths in chunks, 0: default), "oneshot_max_bytes", "sym_min_bytes" (smallest message that
+ * takes the exchange through symmetric memory, 0: never), "sym_multicast" (1: reduce inside the
+ * switch where a multicast mapping exists, 0: plain peer loads).
  * The reference fixes these at compile time (communicator.h:57-58, impl.h:375-376).
  */
 int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value);
@@ -241,7 +243,8 @@ int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns);
 /*
  * Copies the workspace's device status words to `out` (synchronises the device):
  * out[0] = 0 ok / 1 wait timed out / 2 poll cap reached, out[1] = rank, out[2] = CTA,
- * out[3] = stage (0 one-shot, 1 scatter, 2 gather, 3 self-test), out[4] = peer whose data was
+ * out[3] = stage (0 one-shot, 1 scatter, 2 gather, 3 self-test, 4 / 5 the two flags of the
+ * exchange through symmetric memory), out[4] = peer whose data was
  * awaited, out[5] = thread, out[6] = word seen.  Returns GPUK_ERR_PEER_TIMEOUT if out[0] != 0.
  * The reference spins forever instead (communicator.h:98-99).
  */
@@ -280,7 +283,7 @@ int gpuk_emulated_allreduce_rms(gpuk_ws *const *ws, int world_size, void *const 
  * fail or disturb that arena.  It needs no workspaces: the staging memory is a fixed array
  * built into the library (about 8.5 MiB, held by every GPU that loads the library until the
  * process exits), which limits a message to 32 KiB per emulated rank (numel * element size);
- * larger requests return GPUK_ERR_TOO_LARGE.  Rows longer than 2048 16-byte vectors are not
+ * larger requests return GPUK_ERR_TOO_LARGE.  Rows longer than 4096 16-byte vectors are not
  * built.  The first call on a device sets the array up (and synchronises): make it before any
  * stream capture.  All calls on a device share the array, which keeps the protocol's call
  * counter between calls; calls that overlap on the GPU race, so issue them one after another.

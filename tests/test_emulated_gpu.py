@@ -67,25 +67,24 @@ def test_two_shot_many_chunks_per_cta(world, lead_push, lead_reduce):
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("rows_per_chunk", [1, 3])
 @pytest.mark.parametrize("tokens,hidden,quant", [(1, 4096, 3), (129, 1024, 1), (700, 2048, 3), (37, 7168, 4), (1500, 1024, 0)])
-def test_two_shot_with_specialised_roles(world, rows_per_chunk, tokens, hidden, quant):
-    """Push, reduce+gather and epilogue in separate CTAs that meet only through flags."""
+def test_two_shot_rows_per_chunk_and_repeated_calls(world, rows_per_chunk, tokens, hidden, quant):
+    """Chunks of one and of three rows (the last chunk ragged), twice on the same workspace."""
     parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 7 + tokens)
     static = 0.05 if quant == 4 else None
     with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
-        g.set_option("roles", 3)
         g.set_option("rows_per_chunk", rows_per_chunk)
-        for _ in range(2):      # twice: the epoch must advance consistently
+        for _ in range(2):      # twice: the call counter and the staging parity must advance consistently
             outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=TWO_SHOT)
     want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
     _check_all_ranks(outs, want, quant)
 
 
-def test_plain_allreduce_with_specialised_roles():
+def test_plain_allreduce_with_three_rows_per_chunk():
     g0 = torch.Generator().manual_seed(11)
     parts = [torch.randn(300 * 1024 + 64, generator=g0).to(torch.bfloat16) for _ in range(4)]
     want = eo.allreduce_t1(parts)
     with util.EmulatedGroup(4) as g:
-        g.set_option("roles", 3)
+        g.set_option("rows_per_chunk", 3)
         outs = g.plain([p.cuda() for p in parts], force_mode=TWO_SHOT)
     for got in outs:
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
