@@ -263,8 +263,17 @@ const char *gpuk_status_string(int status) {
 // ---------------------------------------------------------------------------------------
 // planning (pure host arithmetic)
 // ---------------------------------------------------------------------------------------
+static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int sm_count, int ctas_per_sm_limit,
+                     int64_t oneshot_max_bytes, bool allow_cluster, gpuk_plan *out);
+
 int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype, int sm_count,
                             int ctas_per_sm_limit, int64_t oneshot_max_bytes, gpuk_plan *out) {
+    return plan_call(world_size, numel, hidden, dtype, sm_count, ctas_per_sm_limit, oneshot_max_bytes, true, out);
+}
+
+// allow_cluster = false: every row stays in one CTA (the exchange through symmetric memory)
+static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int sm_count, int ctas_per_sm_limit,
+                     int64_t oneshot_max_bytes, bool allow_cluster, gpuk_plan *out) {
     if (!out) return fail(GPUK_ERR_INVALID_ARGUMENT, "plan: out is null");
     const int es = elem_size(dtype);
     if (!es) return fail(GPUK_ERR_UNSUPPORTED, "plan: unknown dtype %d", dtype);
@@ -292,10 +301,10 @@ int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype
     if (oneshot_max_bytes <= 0) oneshot_max_bytes = world_size > 1 ? default_oneshot_max_bytes(world_size) : 0;
     const bool one_shot = world_size > 1 && bytes <= std::min(oneshot_max_bytes, kOneShotSlotBytes) && rows <= kMaxBlocks;
     const bool latency = rows <= sm_count;
-    // One-shot with few rows: a row is split over the CTAs of a thread-block cluster so that the
-    // exchange runs on many SMs, as long as a CTA keeps at least 128 vectors.
+    // Few rows: a row is split over the CTAs of a thread-block cluster so that the exchange runs on
+    // many SMs, as long as a CTA keeps at least 128 vectors.
     int cluster = 1;
-    if (one_shot && fused) {
+    if (world_size > 1 && fused && allow_cluster) {
         while (cluster < 8 && (row_vecs + 2 * cluster - 1) / (2 * cluster) >= 128 && rows * 2 * cluster <= 2ll * sm_count) cluster *= 2;
         static const int env_cluster = [] { const char *e = getenv("GPUK_CLUSTER"); return e ? atoi(e) : 0; }();
         if (env_cluster == 1 || env_cluster == 2 || env_cluster == 4 || env_cluster == 8) cluster = env_cluster;
@@ -720,6 +729,9 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
                         (long long)plan.message_bytes, (long long)ws->sym_cap);
         sym = (ws->sym_mc && ws->sym_use_mc && !emulated) ? 2 : 1;
         force_mode = GPUK_MODE_TWO_SHOT;
+        rc = plan_call(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, 1, false, &plan);
+        if (rc) return rc;
+        one_shot = false;
     }
     if (force_mode == 1) {
         if (plan.message_bytes > ws->os_slot_bytes || plan.rows > kMaxBlocks)

@@ -159,7 +159,7 @@ struct ArParams {
     int rows;
     int row_vecs;
     int rows_per_chunk;    // rows a CTA moves through one stage before it turns to the next stage
-    int seg_vecs;          // one-shot: vectors of a row held by one CTA of the cluster that owns the row
+    int seg_vecs;          // vectors of a row held by one CTA of the cluster that owns the row (all of them without a cluster)
     int lead_push;         // two-shot: chunks by which the scatter runs ahead of the reduction (>= 1)
     int lead_reduce;       // two-shot: chunks by which the reduction runs ahead of the epilogue (>= 1)
     EpilogueArgs ep;       // fused only
@@ -209,15 +209,20 @@ __device__ __forceinline__ uint4 sum_in_rank_order(const uint4 (&part)[NR]) {
 // to back before anything is consumed: a step exposes one memory round trip instead of three.
 template <typename T, int NR, int VPT, bool FUSED>
 __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int row_a, int row_b, int row_c,
-                                              EpilogueSmem &sm, int &parity, float static_scale) {
-    constexpr int IBB = (VPT + NR - 1) / NR;     // slice vectors per thread: vpr <= VPT * blockDim / NR
+                                              int cl_rank, int cl_size, EpilogueSmem &sm, int &parity, float static_scale) {
+    constexpr int IBB = (VPT + NR - 1) / NR;     // slice vectors per thread: a CTA's share of vpr <= VPT * blockDim / NR
     const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
     char *mine = p.peer_data[p.rank] + ts;
     uint4 *ag = reinterpret_cast<uint4 *>(mine + p.ag_off);
     const int B = blockDim.x;
-    const int len_a = row_a >= 0 ? row_len(p, row_a) : 0;
+    // this CTA's segment of a row (the whole row unless a cluster shares it) and its share of the slice
+    const int v0 = cl_rank * p.seg_vecs;
+    const int sub = (p.vpr + cl_size - 1) / cl_size, vl0 = cl_rank * sub;
+    const int vl1 = vl0 + sub < p.vpr ? vl0 + sub : p.vpr;
+    auto seg_end = [&](int len) { return v0 + p.seg_vecs < len ? v0 + p.seg_vecs : len; };
+    const int end_a = row_a >= 0 ? seg_end(row_len(p, row_a)) : 0;
     const int len_b = row_b >= 0 ? row_len(p, row_b) : 0;
-    const int len_c = row_c >= 0 ? row_len(p, row_c) : 0;
+    const int end_c = row_c >= 0 ? seg_end(row_len(p, row_c)) : 0;
     const int64_t base_a = static_cast<int64_t>(row_a) * p.row_vecs;
     const int64_t base_b = static_cast<int64_t>(row_b) * p.row_vecs;
     const int64_t base_c = static_cast<int64_t>(row_c) * p.row_vecs;
@@ -228,8 +233,8 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
     int owner[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int v = threadIdx.x + i * B;
-        owner[i] = v < len_a ? v / p.vpr : p.rank;     // my own slice is summed straight from `in`
+        const int v = v0 + threadIdx.x + i * B;
+        owner[i] = v < end_a ? v / p.vpr : p.rank;     // my own slice is summed straight from `in`
         if (owner[i] != p.rank) a[i] = ld_stream(in + base_a + v);
     }
     // ---- issue: reduction
@@ -237,8 +242,8 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
     bool have[IBB];
 #pragma unroll
     for (int b = 0; b < IBB; ++b) {
-        const int vl = threadIdx.x + b * B;
-        have[b] = vl < p.vpr && p.rank * p.vpr + vl < len_b;
+        const int vl = vl0 + threadIdx.x + b * B;
+        have[b] = vl < vl1 && p.rank * p.vpr + vl < len_b;
         if (have[b]) {
 #pragma unroll
             for (int s2 = 0; s2 < NR; ++s2)
@@ -250,10 +255,10 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
     uint4 x[VPT], res[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int v = threadIdx.x + i * B;
-        x[i] = v < len_c ? ld_poll(ag + base_c + v) : make_uint4(0, 0, 0, 0);
+        const int v = v0 + threadIdx.x + i * B;
+        x[i] = v < end_c ? ld_poll(ag + base_c + v) : make_uint4(0, 0, 0, 0);
     }
-    const RowSeg seg = whole_row(p.row_vecs);
+    const RowSeg seg = RowSeg{v0, end_c, cl_rank, cl_size};
     if constexpr (FUSED) {
         if (row_c >= 0) load_residual<T, VPT>(p.ep, seg, row_c, res);
     }
@@ -261,7 +266,7 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
     // ---- consume: scatter
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-        const int v = threadIdx.x + i * B;
+        const int v = v0 + threadIdx.x + i * B;
         if (owner[i] != p.rank) {
             char *slot = p.peer_data[owner[i]] + ts + p.rank * p.rs_slot_bytes;
             st_peer(reinterpret_cast<uint4 *>(slot) + static_cast<int64_t>(row_a) * p.vpr + (v - owner[i] * p.vpr), payload<T>(a[i]));
@@ -271,7 +276,7 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
 #pragma unroll
     for (int b = 0; b < IBB; ++b) {
         if (have[b]) {
-            const int vl = threadIdx.x + b * B;
+            const int vl = vl0 + threadIdx.x + b * B;
 #pragma unroll
             for (int s2 = 0; s2 < NR; ++s2) {
                 if (s2 != p.rank) {
@@ -293,8 +298,8 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
     if (row_c >= 0) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int v = threadIdx.x + i * B;
-            if (v < len_c) {
+            const int v = v0 + threadIdx.x + i * B;
+            if (v < end_c) {
                 x[i] = wait_landed(ag + base_c + v, x[i], p.st, p.rank, kStageGather, v / p.vpr);
                 st_empty(ag + base_c + v);
             }
@@ -305,8 +310,8 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
         } else {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * B;
-                if (v < len_c) st_stream(reinterpret_cast<uint4 *>(p.out) + base_c + v, x[i]);
+                const int v = v0 + threadIdx.x + i * B;
+                if (v < end_c) st_stream(reinterpret_cast<uint4 *>(p.out) + base_c + v, x[i]);
             }
         }
     }
@@ -349,9 +354,12 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
         // s - lead_push - lead_reduce, row by row, so that traffic for later chunks is on the wire
         // while the epilogue of an earlier one runs.  Nothing waits for anything but its own input
         // vectors.
-        const int nk = vb < nchunks ? (nchunks - vb + nb - 1) / nb : 0;
-        auto r0_of = [&](int k) { return (vb + k * nb) * R; };
-        auto r1_of = [&](int k) { const int r1 = (vb + k * nb) * R + R; return r1 < p.rows ? r1 : p.rows; };
+        // With few rows a thread-block cluster shares every row of its chunks, as in the one-shot exchange.
+        const int cl = cluster_size(), cr = cluster_cta_rank();
+        const int ncl = nb / cl, cid = vb / cl;
+        const int nk = cid < nchunks ? (nchunks - cid + ncl - 1) / ncl : 0;
+        auto r0_of = [&](int k) { return (cid + k * ncl) * R; };
+        auto r1_of = [&](int k) { const int r1 = (cid + k * ncl) * R + R; return r1 < p.rows ? r1 : p.rows; };
         // a lead beyond the CTA's own chunks means "finish the earlier role first"
         const int lp = p.lead_push < nk ? p.lead_push : nk, lr = p.lead_reduce < nk ? p.lead_reduce : nk;
         const int steps = nk > 0 ? nk + lp + lr : 0;
@@ -363,7 +371,7 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
                 const int rb = do_b && r0_of(kr) + rr < r1_of(kr) ? r0_of(kr) + rr : -1;
                 const int rc = do_c && r0_of(kf) + rr < r1_of(kf) ? r0_of(kf) + rr : -1;
                 if (ra >= 0 || rb >= 0 || rc >= 0)
-                    two_shot_step<T, NR, VPT, FUSED>(p, ts, ra, rb, rc, sm, parity, static_scale);
+                    two_shot_step<T, NR, VPT, FUSED>(p, ts, ra, rb, rc, cr, cl, sm, parity, static_scale);
             }
         }
     } else {
