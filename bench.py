@@ -36,10 +36,11 @@ if ROOT not in sys.path:
 
 L2_BYTES = 126 << 20
 NVLINK_PEER_COPY_GBS = 770.0      # measured peer copy per direction on this pool (nominal 900)
+NVLINK_SM_STORE_GBS = 690.0       # measured here: SM-issued 16-byte peer stores, both directions busy (copy engine: 754)
 HBM_FALLBACK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the one-GPU kernel per token at hidden 8192, from the
-# ncu capture summarised in profiles/ (189.7 MB per launch of 4096 tokens; traffic grows with the tokens)
-K1_DRAM_TRAFFIC_BYTES_PER_TOKEN_H8192 = 189.7e6 / 4096
+# ncu capture summarised in profiles/ (185.0 MB per launch of 4096 tokens; traffic grows with the tokens)
+K1_DRAM_TRAFFIC_BYTES_PER_TOKEN_H8192 = 185.0e6 / 4096
 
 
 def measured_hbm_peak():
@@ -464,7 +465,7 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    head = run_config(cfg, env, gpuk, rank, world, args.steps, args.warmup, barrier, native=True, graph=cfg.tokens <= 64)
+    head = run_config(cfg, env, gpuk, rank, world, args.steps, args.warmup, barrier, native=True, graph=True)
     # keep the same kernel running a little longer so the 100 ms clock sampler sees it under load
     extra = max(0, int(0.4 / max(head["us_per_call"] * 1e-6, 1e-7)) - args.steps)
     if extra:
@@ -512,6 +513,7 @@ def main():
             roof = {"bound": "nvlink", "achieved": ach, "peak": NVLINK_PEER_COPY_GBS, "unit": "GB/s",
                     "frac": ach / NVLINK_PEER_COPY_GBS, "traffic": None,
                     "peak_kind": "of measured peer copy per direction (nominal 900)",
+                    "frac_of_sm_store_peak": ach / NVLINK_SM_STORE_GBS,
                     "algorithmic_bytes_per_launch": bus_bytes(cfg.tokens, cfg.hidden, world),
                     "kernel": "ar_kernel (two-shot, fused epilogue)"}
         line = {

@@ -160,12 +160,13 @@ int elem_size(int dtype) {
 bool valid_world(int w) { return w == 2 || w == 4 || w == 8; }
 
 int64_t default_oneshot_max_bytes(int world) {
-    // The reference's rule is impl.h:375-376.  Two ranks: measured, one-shot wins up to the largest
-    // one-shot slot (10.0 vs 13.5 us at 2 MiB); four and eight ranks: see the crossover table of the bench.
+    // The reference's rule is impl.h:375-376.  Measured on B200 at hidden 8192 (CUDA-graph replay, us per
+    // call, one-shot / two-shot): two ranks 10.0 / 13.5 at 2 MiB; eight ranks 12.3 / 15.5 at 256 KiB,
+    // 15.5 / 16.1 at 512 KiB, 20.8 / 14.3 at 1 MiB.  Four ranks: between the two.
     switch (world) {
     case 2: return 2 << 20;
-    case 4: return 512 << 10;
-    default: return 256 << 10;
+    case 4: return 1 << 20;
+    default: return 512 << 10;
     }
 }
 
