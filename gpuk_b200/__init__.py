@@ -296,3 +296,64 @@ class GPUKDistEnv:
         self._o.allreduce_rms(self.fptr or 0, allreduce_in, residual_in, rms_weight, residual_out, norm_out,
                               scale_out, eps, qt)
         return residual_out, norm_out, scale_out
+
+    def allreduce_add_rms_fused_host(self, allreduce_in, residual_in, rms_weight, eps, out, *, chunks: int = 4,
+                                     static_scale: Optional[torch.Tensor] = None, quant_type: Optional[int] = None):
+        """The fused call for inputs and results that live in pinned host memory.
+
+        ``allreduce_in`` and ``residual_in`` are pinned CPU tensors ``[tokens, hidden]``; ``out`` is a triple
+        of pinned CPU tensors ``(residual_out, norm_out as FP8 or uint8, scale_out [tokens, 1] fp32)`` that
+        receives the results.  The rows are cut into ``chunks`` pieces that travel as a pipeline over three
+        streams -- host-to-device copy of piece i + 1, the fused kernel on piece i, device-to-host copy of piece
+        i - 1 -- so the two directions of the host link are busy at the same time.  Rows are independent, so
+        the results are those of one call on the whole tensor.  Returns after the last copy has completed.
+        Every rank must call it with the same shapes and the same ``chunks``.  The reference has no
+        counterpart: its callers keep activations on the device.
+        """
+        self._require_workspace()
+        tokens, hidden = allreduce_in.shape
+        dev = torch.device("cuda", self.device_id)
+        key = (tokens, hidden, allreduce_in.dtype, out[1].dtype)
+        st = getattr(self, "_host_path", None)
+        if st is None or st["key"] != key:
+            st = self._host_path = {
+                "key": key,
+                "x": torch.empty(tokens, hidden, dtype=allreduce_in.dtype, device=dev),
+                "r": torch.empty(tokens, hidden, dtype=allreduce_in.dtype, device=dev),
+                "res_out": torch.empty(tokens, hidden, dtype=allreduce_in.dtype, device=dev),
+                "norm_out": torch.empty(tokens, hidden, dtype=out[1].dtype, device=dev),
+                "scale": torch.empty(tokens, 1, dtype=torch.float32, device=dev),
+                "s_in": torch.cuda.Stream(device=dev), "s_out": torch.cuda.Stream(device=dev),
+            }
+        if static_scale is not None:
+            qt = QUANT_STATIC_E4M3FN_448
+            scale_dev = static_scale.reshape(-1)
+        else:
+            qt = fp8_policy_id if quant_type is None else quant_type
+            scale_dev = None
+        cur = torch.cuda.current_stream(dev)
+        s_in, s_out = st["s_in"], st["s_out"]
+        s_in.wait_stream(cur)
+        s_out.wait_stream(cur)
+        chunks = max(1, min(int(chunks), tokens))
+        step = (tokens + chunks - 1) // chunks
+        for lo in range(0, tokens, step):
+            hi = min(lo + step, tokens)
+            with torch.cuda.stream(s_in):
+                st["x"][lo:hi].copy_(allreduce_in[lo:hi], non_blocking=True)
+                st["r"][lo:hi].copy_(residual_in[lo:hi], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            cur.wait_event(ready)
+            self._o.allreduce_rms(self.fptr or 0, st["x"][lo:hi], st["r"][lo:hi], rms_weight, st["res_out"][lo:hi],
+                                  st["norm_out"][lo:hi], scale_dev if scale_dev is not None else st["scale"][lo:hi], eps, qt)
+            done = torch.cuda.Event()
+            done.record(cur)
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                out[0][lo:hi].copy_(st["res_out"][lo:hi], non_blocking=True)
+                out[1][lo:hi].copy_(st["norm_out"][lo:hi], non_blocking=True)
+                if scale_dev is None:
+                    out[2][lo:hi].copy_(st["scale"][lo:hi], non_blocking=True)
+        s_out.synchronize()
+        return out

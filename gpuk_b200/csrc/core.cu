@@ -322,7 +322,7 @@ static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int s
         if (!fused) { vpt = 4; threads = std::max(32, ((row_vecs + 3) / 4 + 31) / 32 * 32); }
     }
     int per_sm = std::max(1, std::min(4, 1024 / threads));
-    // tuning knobs for experiments (read once): CTAs per SM and rows per flag exchange
+    // tuning knobs for experiments (read once): CTAs per SM and rows per pipeline chunk
     static const int env_per_sm = [] { const char *e = getenv("GPUK_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
     static const int env_rpc = [] { const char *e = getenv("GPUK_ROWS_PER_CHUNK"); return e ? atoi(e) : 0; }();
     if (env_per_sm > 0) per_sm = std::min(per_sm, env_per_sm);

@@ -200,7 +200,7 @@ typedef struct gpuk_plan {
     int one_shot;       /* 1: one-shot exchange, 0: two-shot */
     int vpt;            /* 16-byte vectors of a row held per thread */
     int threads;        /* CTA size */
-    int rows_per_chunk; /* rows between two flag exchanges (two-shot) */
+    int rows_per_chunk; /* rows a CTA takes through one pipeline role at a time (two-shot) */
     int grid;           /* CTAs per rank */
     int rows;
     int row_vecs;

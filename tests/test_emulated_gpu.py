@@ -1,5 +1,5 @@
 """The N-rank kernels on ONE GPU: all ranks of a group run inside one cooperative launch
-(gpuk_emulated_allreduce_rms), so the exchange logic, the flag protocol and the fused
+(gpuk_emulated_allreduce_rms), so the exchange logic, the self-announcing staging protocol and the fused
 epilogue are checked against the T1 oracle without needing N GPUs."""
 import pytest
 import torch
@@ -92,7 +92,7 @@ def test_plain_allreduce_with_three_rows_per_chunk():
 
 def test_back_to_back_calls_mixed_shapes_and_modes():
     """One workspace, a sequence of calls that changes shape and exchange mode: exercises the
-    epoch counter, the one-shot double buffer and staging reuse."""
+    call counter, the double-buffered staging and its reuse."""
     world = 4
     seq = [(8, 2048, ONE_SHOT), (8, 2048, ONE_SHOT), (8, 2048, ONE_SHOT), (300, 1024, TWO_SHOT), (8, 2048, ONE_SHOT),
            (64, 4096, TWO_SHOT), (64, 4096, TWO_SHOT), (3, 1024, ONE_SHOT), (700, 1024, TWO_SHOT), (1, 8192, ONE_SHOT)]

@@ -107,6 +107,30 @@ def test_through_the_operator_library_with_a_group_of_one():
     util.check_against_oracle((res_out.cpu(), norm_out.cpu(), scale.cpu()), want, 3)
 
 
+@pytest.mark.parametrize("tokens,chunks,static", [(1000, 4, None), (37, 8, None), (5, 16, None), (256, 3, 0.05)])
+def test_host_buffer_api_pipelines_row_pieces(tokens, chunks, static):
+    """GPUKDistEnv.allreduce_add_rms_fused_host: pinned host tensors in, pinned host tensors out, rows
+    cut into pieces (the last one ragged, more pieces than rows clamps) -- same results as one call."""
+    import torch.distributed as dist
+    import gpuk_b200
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29571")
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    env = gpuk_b200.GPUKDistEnv(group=None, device_id=0)
+    parts, res, w = util.random_case(1, tokens, 2048, torch.bfloat16, seed=tokens + chunks)
+    out = (torch.empty_like(res).pin_memory(), torch.empty(res.shape, dtype=torch.float8_e4m3fn).pin_memory(),
+           torch.full((tokens, 1), -1.0).pin_memory())
+    st = None if static is None else torch.tensor([static], dtype=torch.float32, device="cuda")
+    for _ in range(2):   # second call reuses the cached device buffers and streams
+        env.allreduce_add_rms_fused_host(parts[0].pin_memory(), res.pin_memory(), w.cuda(), 1e-6, out, chunks=chunks,
+                                         static_scale=st)
+    quant = 4 if static is not None else 3
+    want = eo.add_rms_quant(parts[0], res, w, 1e-6, quant, static)
+    got = (out[0], out[1], out[2] if static is None else torch.tensor([static]))
+    util.check_against_oracle(got, want, quant)
+
+
 @pytest.mark.parametrize("name,rows", [("c2", None), ("c3", None), ("c4", 16384), ("c5", None)])
 def test_benchmark_configs_full_size(name, rows):
     """Full benchmark shapes.  The oracle checks a sample of rows; size-independent properties

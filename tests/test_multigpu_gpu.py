@@ -161,6 +161,15 @@ def _ipc_worker(rank, world, port, cases, q):
                 assert torch.equal(plain.cpu().view(torch.int16), eo.allreduce_t1(parts).view(torch.int16))
             except AssertionError as e:   # pragma: no cover
                 failures.append(f"case {i} {tokens}x{hidden}: {e}")
+        # host-buffer API: rows pipelined in pieces, every piece a full exchange
+        parts, res, w = util.random_case(world, 300, 4096, torch.bfloat16, seed=777)
+        out = (torch.empty_like(res).pin_memory(), torch.empty(res.shape, dtype=torch.float8_e4m3fn).pin_memory(),
+               torch.empty(300, 1).pin_memory())
+        env.allreduce_add_rms_fused_host(parts[rank].pin_memory(), res.pin_memory(), w.cuda(), 1e-6, out, chunks=4)
+        try:
+            util.check_against_oracle(out, eo.epilogue_t1(parts, res, w, 1e-6, 3), 3)
+        except AssertionError as e:   # pragma: no cover
+            failures.append(f"host api: {e}")
         if env.multicast:
             # The same exchange reduced inside the NVSwitch.  The switch rounds 16-bit sums its own way
             # (ties away from zero), so about one sum in seven is off by one unit in the last place:
