@@ -1,6 +1,8 @@
 // Definitions behind launch.cuh; included only by the per-type translation units.
 #pragma once
 
+#include <mutex>
+
 #include "launch.cuh"
 
 namespace gpuk {
@@ -73,12 +75,15 @@ static cudaError_t launch_staged_one(const NormQuantParams &p, int threads, int 
     const size_t smem = static_cast<size_t>(STAGES) * 2 * p.ep.row_vecs * 16;
     if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
     // per device: opt in to the shared-memory size and look up how many CTAs fit an SM
+    // (this entry point has no workspace to keep the cache in, so it is guarded for concurrent callers)
+    static std::mutex cache_mutex;
     static int per_sm_by_device[64] = {};
     static size_t smem_by_device[64] = {};
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return e;
     if (device < 0 || device >= 64) return cudaErrorInvalidConfiguration;
+    std::lock_guard<std::mutex> lock(cache_mutex);
     if (per_sm_by_device[device] == 0 || smem_by_device[device] != smem) {
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
