@@ -1,8 +1,8 @@
 """Generate golden vectors by running the reference's own Python on CPU ranks (gloo).
 
-Run in a container that has the reference checkout (default ``/root/reference``):
+Run where a checkout of the reference project is available (``--ref`` names its directory):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference checkout>]
 
 The reference module ``gpuk/__init__.py`` loads a CUDA library at import time and binds
 ``torch.ops.gpuk.*`` names (``gpuk/__init__.py:10-35``).  Neither is needed for
