@@ -90,3 +90,25 @@ def test_plan_tiles_cover_every_legal_row():
         assert p.vpt in (1, 2, 4, 8) and p.threads % 32 == 0 and p.threads <= (512 if p.vpt >= 4 else 1024)
         assert p.cluster in (1, 2, 4, 8) and p.grid % p.cluster == 0
         assert p.vpt * p.threads * p.cluster >= p.row_vecs == hidden // 8
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_plan_tiles_respect_the_kernels_launch_bounds(world):
+    """The kernels are compiled for at most 256 threads per CTA in the two-shot exchange (512 for the
+    8-vector tile) and 1024 / 256 / 512 in the one-shot exchange (kernels.cuh: ar_max_threads); a plan
+    beyond that would fail at launch.  Also: the grid is whole clusters, a cluster covers its row."""
+    for hidden in list(range(8, 4096, 8 * 7)) + list(range(4096, 32768 + 1, 8 * 61)) + [1024, 2048, 4096, 7168, 8192, 16384, 32768]:
+        for tokens in (1, 7, 8, 32, 64, 148, 149, 300, 1024, 5000):
+            for crossover in (1, 1 << 40):
+                p = cabi.plan(world, tokens * hidden, hidden, oneshot_max_bytes=crossover)
+                limit = (512 if p.vpt == 8 else 256) if not p.one_shot else {1: 1024, 2: 1024, 4: 256, 8: 512}[p.vpt]
+                assert 32 <= p.threads <= limit and p.threads % 32 == 0, (hidden, tokens, crossover, p.threads, p.vpt)
+                assert p.cluster in (1, 2, 4, 8) and p.grid % p.cluster == 0 and p.grid >= p.cluster
+                seg = -(-p.row_vecs // p.cluster)
+                assert p.vpt * p.threads >= seg and seg * p.cluster >= p.row_vecs
+                assert p.grid // p.cluster <= -(-p.rows // p.rows_per_chunk)
+                assert p.lead_push >= 1 and p.lead_reduce >= 1
+
+
+def test_attach_symmetric_validates_before_touching_cuda():
+    assert cabi.lib.gpuk_ws_attach_symmetric(None, None, 2, None, 1 << 20) == cabi.ERR_INVALID_ARGUMENT
