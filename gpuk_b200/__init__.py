@@ -130,6 +130,7 @@ class GPUKDistEnv:
         self._IS_CAPTURING = False
         self._IS_CAPTURED = False
         self.disabled = False
+        self.multicast = False     # True once a symmetric buffer with an NVSwitch multicast mapping is attached
         self._o.set_device(self.device_id)
 
         if self.world_size == 1:
@@ -149,7 +150,6 @@ class GPUKDistEnv:
         self._o.open_ar_fusion_barrier_handles(self.fptr, barrier_handle_list)
         self._o.open_ar_fusion_data_handles(self.fptr, data_handle_list)
         self.barrier()
-        self.multicast = False
         if symmetric_bytes is None and os.environ.get("GPUK_SYMMETRIC_BYTES"):
             symmetric_bytes = int(os.environ["GPUK_SYMMETRIC_BYTES"])
         if symmetric_bytes:
