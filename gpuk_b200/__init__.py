@@ -172,6 +172,16 @@ class GPUKDistEnv:
         self.multicast = bool(mc)
         self.barrier()
 
+    def check(self) -> None:
+        """Synchronises the device and raises if a wait of an earlier fused call gave up on a peer
+        (``gpuk_ws_status``): the message names the rank, CTA, stage and peer that was waited for.
+        The reference has no counterpart; its waits spin for ever (``communicator.h:98-99``)."""
+        import ctypes
+        if self.fptr:
+            out = (ctypes.c_uint32 * 8)()
+            if cabi.lib.gpuk_ws_status(ctypes.c_void_p(self.fptr), out) != cabi.OK:
+                raise RuntimeError(cabi.last_error())
+
     def set_option(self, name: str, value: int) -> None:
         """Tuning options of the workspace (``gpuk_ws_set_option``); every rank must set the same."""
         import ctypes
