@@ -38,7 +38,9 @@ _OPS = [
     "fused_rope_rms_2way",
 ]
 
-# name, world, tokens, hidden, dtype, fp8 flavour (None = no quantisation), fp8 max, seed
+# name, world, tokens, hidden, dtype, fp8 flavour (None = no quantisation), fp8 max, seed[, input distribution]
+# input distribution: absent = N(0,1) partials; "outliers" = 0.1 % of the partials' elements times 20 (the
+# prefill benchmark's inputs); "div_sqrt8" = partials N(0,1) / sqrt(8) (the decode benchmark's inputs)
 CASES = [
     ("n2_bf16_16x1024_fn240", 2, 16, 1024, "bfloat16", "float8_e4m3fn", 240, 11),
     ("n2_bf16_16x1024_fnuz120", 2, 16, 1024, "bfloat16", "float8_e4m3fnuz", 120, 12),
@@ -49,6 +51,8 @@ CASES = [
     ("n2_bf16_3x7168_fn448", 2, 3, 7168, "bfloat16", "float8_e4m3fn", 448, 17),
     ("n4_bf16_8x1024_fn448", 4, 8, 1024, "bfloat16", "float8_e4m3fn", 448, 18),
     ("n8_bf16_4x2048_fn448", 8, 4, 2048, "bfloat16", "float8_e4m3fn", 448, 19),
+    ("n2_bf16_3x8192_fn448_outliers", 2, 3, 8192, "bfloat16", "float8_e4m3fn", 448, 20, "outliers"),
+    ("n2_bf16_2x8192_fn448_div_sqrt8", 2, 2, 8192, "bfloat16", "float8_e4m3fn", 448, 21, "div_sqrt8"),
 ]
 
 
@@ -75,21 +79,27 @@ def _bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().numpy()
 
 
-def make_inputs(world, tokens, hidden, dtype, seed):
+def make_inputs(world, tokens, hidden, dtype, seed, distribution=None):
     g = torch.Generator().manual_seed(seed)
-    parts = [torch.randn(tokens, hidden, generator=g).to(dtype) for _ in range(world)]
+    parts = [torch.randn(tokens, hidden, generator=g) for _ in range(world)]
+    if distribution == "outliers":
+        parts = [torch.where(torch.rand(tokens, hidden, generator=g) < 0.001, x * 20.0, x) for x in parts]
+    elif distribution == "div_sqrt8":
+        parts = [x / 8.0 ** 0.5 for x in parts]
+    parts = [x.to(dtype) for x in parts]
     residual = torch.randn(tokens, hidden, generator=g).to(dtype)
     weight = (1.0 + 0.1 * torch.randn(hidden, generator=g)).to(dtype)
     return parts, residual, weight
 
 
 def worker(rank, world, port, ref_root, case, out_dir):
-    name, _, tokens, hidden, dtype_s, fp8_s, fp8_max, seed = case
+    name, _, tokens, hidden, dtype_s, fp8_s, fp8_max, seed = case[:8]
+    distribution = case[8] if len(case) > 8 else None
     torch.set_num_threads(1)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     mod, _lib = load_reference(ref_root)
     dtype = getattr(torch, dtype_s)
-    parts, residual, weight = make_inputs(world, tokens, hidden, dtype, seed)
+    parts, residual, weight = make_inputs(world, tokens, hidden, dtype, seed, distribution)
     if fp8_s is not None:
         mod.fp8 = getattr(torch, fp8_s)
         mod.fp8_max_val = fp8_max
@@ -120,9 +130,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference")
     ap.add_argument("--out", default=HERE)
+    ap.add_argument("--only", default=None, help="generate only the cases whose name contains this text")
     args = ap.parse_args()
     port = 29710
     for case in CASES:
+        if args.only and args.only not in case[0]:
+            continue
         mp.spawn(worker, args=(case[1], port, args.ref, case, args.out), nprocs=case[1], join=True)
         port += 1
 

@@ -43,7 +43,7 @@ def load_golden(path):
 
 
 def test_golden_fixtures_present():
-    assert len(GOLDEN) >= 9
+    assert len(GOLDEN) >= 11
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
