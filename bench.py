@@ -3,6 +3,8 @@
     python bench.py --gpus 1 --steps K --warmup W
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...        # the reference's CPU path on the host cores
+    python bench.py --case norm_quant --tokens 4096 --hidden 8192 --iters 6     # short run to put under ncu
+    python bench.py --case emulated --world 8 --mode 2 --tokens 1024 --hidden 8192 --iters 4
 
 A step is ONE call of the fused operator on the headline workload, config 3 of the
 baseline: per-rank bf16 partial [1024, 8192], residual [1024, 8192], weight [8192],
@@ -11,17 +13,23 @@ no-communication kernel runs on the same shape.  The message (16 MiB) is smaller
 the timed loop rotates over enough distinct buffer sets to exceed L2 several times.
 
 Rank 0 prints one JSON line: `value` is microseconds per call with inputs resident in HBM,
-timed with CUDA events over exactly K calls (max over ranks); `e2e` is the same call through
-the public Python API with the step's inputs copied from pinned host memory and its results
-copied back inside the timed region.  `sweep` holds the other configs (decode 8 x 8192 with a
-static scale, prefill 16384 x 7168 with outliers, the 32 x 8192 message of the decoder model).
+timed with CUDA events over blocks of exactly K calls (max over ranks per block, median over
+blocks; enough blocks to cover 20 ms); `e2e` is the same call through the public Python API
+with the step's inputs copied from pinned host memory and its results copied back inside the
+timed region.  Before a config is timed, one call is compared on every rank with the reference's
+operator sequence applied to the rank-order fp32 sum of the gathered partials (`parity`).
+`sweep` holds the other configs (decode 8 x 8192 with a static scale, prefill 16384 x 7168 with
+outliers, the 32 x 8192 message of the decoder model, the 128 x 4096 shape of the CPU config).
 Inputs are seeded synthetic tensors with the distributions of the baseline configs.
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
+import math
 import os
+import shutil
 import statistics
 import subprocess
 import sys
@@ -35,12 +43,26 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 L2_BYTES = 126 << 20
-NVLINK_PEER_COPY_GBS = 770.0      # measured peer copy per direction on this pool (nominal 900)
-NVLINK_SM_STORE_GBS = 690.0       # measured here: SM-issued 16-byte peer stores, both directions busy (copy engine: 754)
+NVLINK_NOMINAL_GBS = 900.0        # per direction per GPU: the roofline denominator of every multi-GPU number
+NVLINK_PEER_COPY_GBS = 770.0      # measured peer copy per direction on this pool (copy engine)
+NVLINK_SM_STORE_GBS = 690.0       # measured here: SM-issued 16-byte peer stores, both directions busy
 HBM_FALLBACK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the one-GPU kernel per token at hidden 8192, from the
-# ncu capture summarised in profiles/ (185.0 MB per launch of 4096 tokens; traffic grows with the tokens)
-K1_DRAM_TRAFFIC_BYTES_PER_TOKEN_H8192 = 185.0e6 / 4096
+METRIC = "fused_ar_rmsnorm_fp8_us_per_call"
+MIN_TIMED_SECONDS = 0.02
+MAX_BLOCKS = 25
+
+
+def load_workloads():
+    """gpuk_b200/workloads.py loaded by path: it needs nothing of the package, and importing the
+    package would map the CUDA libraries into processes (the CPU arm) that must not touch them."""
+    name = "gpuk_workloads"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "gpuk_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def measured_hbm_peak():
@@ -52,6 +74,20 @@ def measured_hbm_peak():
         return HBM_FALLBACK_GBS, "fallback"
 
 
+def dram_traffic(kernel, tokens, hidden):
+    """DRAM bytes per launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum) from the capture
+    table in profiles/dram_traffic.txt, scaled from the captured case to `tokens` x `hidden`
+    (traffic grows in proportion to the elements).  None when the table has no row for the kernel."""
+    try:
+        for line in open(os.path.join(ROOT, "profiles", "dram_traffic.txt")):
+            f = line.split()
+            if len(f) >= 4 and not line.startswith("#") and f[0] == kernel:
+                return float(f[3]) * (tokens * hidden) / (float(f[1]) * float(f[2]))
+    except Exception:
+        pass
+    return None
+
+
 def hbm_bytes(tokens, hidden):
     """Algorithmic HBM bytes of one call at one GPU: read x, read residual, write residual_out
     (bf16 each), write FP8, write scales, read weight."""
@@ -61,6 +97,14 @@ def hbm_bytes(tokens, hidden):
 def bus_bytes(tokens, hidden, n):
     """NVLink bytes per GPU per direction, all-reduce bus-bandwidth convention."""
     return 2.0 * (n - 1) / n * tokens * hidden * 2
+
+
+def config_dict(cfg, world, **extra):
+    """The `config` object: the same keys in both arms."""
+    quant = {3: "per-token dynamic e4m3fn /448", 4: f"per-tensor static scale {cfg.static_scale} e4m3fn"}[cfg.quant_type]
+    d = {"workload": cfg.name, "tokens": cfg.tokens, "hidden": cfg.hidden, "ranks": world, "quant": quant}
+    d.update(extra)
+    return d
 
 
 # ---------------------------------------------------------------------------------------
@@ -121,11 +165,11 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------
-# workloads
+# workloads, timing, parity
 # ---------------------------------------------------------------------------------------
 def make_sets(cfg, rank, world, nsets, device):
     """`nsets` distinct input/output buffer sets for one config (seeded, config distributions)."""
-    from gpuk_b200 import workloads as oin
+    oin = load_workloads()
     sets = []
     w = oin.make_weight(cfg).to(device)
     base_x = oin.make_partial(cfg, rank, world).to(device)
@@ -148,10 +192,17 @@ def sets_needed(cfg):
     return max(2, min(16, -(-4 * L2_BYTES // per_set)))
 
 
-def time_calls(call, nsets, steps, warmup, barrier):
-    """CUDA-event time of exactly `steps` calls after `warmup` calls; returns seconds."""
-    for i in range(warmup):
-        call(i % nsets)
+def max_over_ranks(seconds, world):
+    if world == 1:
+        return seconds
+    import torch.distributed as dist
+    t = torch.tensor([seconds], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_block(call, nsets, steps, barrier):
+    """CUDA-event time of exactly `steps` calls, bracketed by a barrier and a synchronize; seconds."""
     barrier()
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -164,13 +215,81 @@ def time_calls(call, nsets, steps, warmup, barrier):
     return start.elapsed_time(end) * 1e-3
 
 
-def max_over_ranks(seconds, world):
-    if world == 1:
-        return seconds
+def time_calls(call, nsets, steps, warmup, barrier, world, min_seconds=MIN_TIMED_SECONDS):
+    """`warmup` untimed calls, then blocks of exactly `steps` calls until `min_seconds` are covered
+    (at most MAX_BLOCKS blocks; every rank runs the same number, decided from the first block's
+    max over ranks).  Returns (median over blocks of the max over ranks, number of blocks)."""
+    for i in range(warmup):
+        call(i % nsets)
+    first = max_over_ranks(time_block(call, nsets, steps, barrier), world)
+    blocks = [first]
+    want = max(1, min(MAX_BLOCKS, int(math.ceil(min_seconds / max(first, 1e-9)))))
+    for _ in range(want - 1):
+        blocks.append(max_over_ranks(time_block(call, nsets, steps, barrier), world))
+    return statistics.median(blocks), len(blocks)
+
+
+def native_after_sum(total, residual, w, eps, cfg):
+    """The reference's operator sequence after the collective (gpuk/__init__.py:150-164), in PyTorch."""
+    ro = total + residual
+    v = ro.float().pow(2).mean(-1, keepdim=True)
+    n = w * (ro * torch.rsqrt(v + eps)).to(ro.dtype)
+    if cfg.quant_type == 4:
+        s = torch.tensor([cfg.static_scale], dtype=torch.float32, device=total.device)
+        q = (n.float() / s).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        return ro, q, None
+    s = n.float().abs().amax(-1, keepdim=True) / 448.0
+    s = torch.where(s == 0, torch.ones_like(s), s)
+    q = (n.float() / s).clamp_(-448, 448).to(torch.float8_e4m3fn)
+    return ro, q, s
+
+
+def fp8_step_distance(a, b):
+    """Distance in e4m3 code steps between two FP8 tensors (sign-magnitude codes mapped to a line)."""
+    def line(t):
+        c = t.view(torch.uint8).to(torch.int16)
+        return torch.where(c >= 128, 128 - c, c)
+    return (line(a) - line(b)).abs()
+
+
+def parity_check(cfg, sets, w, rank, world, max_rows=2048):
+    """One call's results on this rank (already in sets[0]) against the reference's PyTorch operators
+    applied to the fp32 rank-order sum of all ranks' partials, rounded once (what the reference's fused
+    kernel computes for the sum, impl.h:242-255).  Bars: residual_out bit-exact, scales within 1e-3
+    relative, FP8 codes within one step on >= 99.9 % of the elements.  A row sample bounds the cost."""
     import torch.distributed as dist
-    t = torch.tensor([seconds], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    x, r, res_out, norm_out, scale = sets[0]
+    rows = min(cfg.tokens, max_rows)
+    idx = torch.linspace(0, cfg.tokens - 1, rows, device=x.device).long().unique()
+    xs = x[idx].contiguous()
+    if world > 1:
+        gathered = [torch.empty_like(xs) for _ in range(world)]
+        dist.all_gather(gathered, xs)
+    else:
+        gathered = [xs]
+    acc = gathered[0].float()
+    for g in gathered[1:]:
+        acc = acc + g.float()
+    total = acc.to(x.dtype)
+    want_ro, want_q, want_s = native_after_sum(total, r[idx], w, cfg.eps, cfg)
+    mism = int((want_ro.view(torch.int16) != res_out[idx].view(torch.int16)).sum().item())
+    d = fp8_step_distance(norm_out[idx], want_q)
+    within1 = float((d <= 1).float().mean().item())
+    exact = float((d == 0).float().mean().item())
+    srel = 0.0
+    if want_s is not None:
+        srel = float(((scale[idx] - want_s).abs() / want_s.abs().clamp_min(1e-30)).max().item())
+        # a 16-bit row maximum that lands on the neighbouring value moves the scale by one 2^-8 step:
+        # count such rows, do not fail on them unless they are more than 0.1 % of the rows
+        srel_rows = float((((scale[idx] - want_s).abs() / want_s.abs().clamp_min(1e-30)) > 1e-3).float().mean().item())
+    else:
+        srel_rows = 0.0
+    ok = mism == 0 and within1 >= 0.999 and srel_rows <= 1e-3
+    flag = torch.tensor([0 if ok else 1], device=x.device)
+    if world > 1:
+        dist.all_reduce(flag)
+    return {"checked_rows": int(idx.numel()), "ok_all_ranks": int(flag.item()) == 0, "residual_mismatches": mism,
+            "fp8_within_1_step": within1, "fp8_identical": exact, "scale_max_rel": srel, "rows_scale_off_frac": srel_rows}
 
 
 def run_config(cfg, env, gpuk, rank, world, steps, warmup, barrier, graph=False, native=False):
@@ -183,8 +302,12 @@ def run_config(cfg, env, gpuk, rank, world, steps, warmup, barrier, graph=False,
         x, r, res_out, norm_out, scale = sets[i]
         gpuk.allreduce_rms(fptr, x, r, w, res_out, norm_out, scale, cfg.eps, cfg.quant_type)
 
-    secs = max_over_ranks(time_calls(call, nsets, steps, warmup, barrier), world)
-    out = {"workload": cfg.name, "us_per_call": secs / steps * 1e6, "buffer_sets": nsets}
+    call(0)
+    torch.cuda.synchronize()
+    barrier()
+    parity = parity_check(cfg, sets, w, rank, world)
+    secs, blocks = time_calls(call, nsets, steps, warmup, barrier, world)
+    out = {"workload": cfg.name, "us_per_call": secs / steps * 1e6, "buffer_sets": nsets, "blocks": blocks, "parity": parity}
     if graph:
         # the same calls replayed from a CUDA graph: launch overhead of the host wrapper removed
         g = torch.cuda.CUDAGraph()
@@ -201,27 +324,23 @@ def run_config(cfg, env, gpuk, rank, world, steps, warmup, barrier, graph=False,
                     call(i)
         torch.cuda.current_stream().wait_stream(s)
         reps = max(1, steps // per_graph)
-        secs_g = max_over_ranks(time_calls(lambda i: g.replay(), 1, reps, max(3, warmup // per_graph), barrier), world)
+        secs_g, _ = time_calls(lambda i: g.replay(), 1, reps, max(3, warmup // per_graph), barrier, world)
         out["us_per_call_graph"] = secs_g / (reps * per_graph) * 1e6
+        del g
     if world > 1 and native:
         # comparison on the same GPUs: NCCL all-reduce + the unfused PyTorch operator sequence
+        import torch.distributed as dist
         x0, r0 = sets[0][0], sets[0][1]
         xn = x0.clone()
 
         def call_native(i):
             xn.copy_(x0)
-            if cfg.quant_type == 4:
-                import torch.distributed as dist
-                dist.all_reduce(xn)
-                ro = xn + r0
-                v = ro.float().pow(2).mean(-1, keepdim=True)
-                n = w * (ro * torch.rsqrt(v + cfg.eps)).to(ro.dtype)
-                (n.float() / cfg.static_scale).clamp_(-448, 448).to(torch.float8_e4m3fn)
-            else:
-                env.allreduce_add_rms_native(xn, r0, w, cfg.eps, True)
+            dist.all_reduce(xn)
+            native_after_sum(xn, r0, w, cfg.eps, cfg)
 
         k = max(5, min(steps, 50))
-        out["us_per_call_nccl_unfused"] = max_over_ranks(time_calls(call_native, 1, k, 3, barrier), world) / k * 1e6
+        secs_n, _ = time_calls(call_native, 1, k, 3, barrier, world, min_seconds=0.0)
+        out["us_per_call_nccl_unfused"] = secs_n / k * 1e6
     us = out.get("us_per_call_graph", out["us_per_call"]) if graph else out["us_per_call"]
     if world == 1:
         gbs = hbm_bytes(cfg.tokens, cfg.hidden) / (out["us_per_call"] * 1e-6) / 1e9
@@ -229,7 +348,7 @@ def run_config(cfg, env, gpuk, rank, world, steps, warmup, barrier, graph=False,
         out.update(hbm_gbs=gbs, frac_of_hbm_peak=gbs / peak)
     else:
         gbs = bus_bytes(cfg.tokens, cfg.hidden, world) / (us * 1e-6) / 1e9
-        out.update(busbw_gbs=gbs, frac_of_nvlink_peak=gbs / NVLINK_PEER_COPY_GBS)
+        out.update(busbw_gbs=gbs, frac_of_nvlink_900=gbs / NVLINK_NOMINAL_GBS)
     del sets
     torch.cuda.empty_cache()
     return out
@@ -239,7 +358,7 @@ def run_e2e(cfg, env, rank, world, steps, warmup, barrier):
     """Public API with host buffers: the step's inputs start in pinned host memory and its three results end
     there (GPUKDistEnv.allreduce_add_rms_fused_host: rows pipelined in pieces over copy-in, kernel and copy-out
     streams); the timed region ends when the last result byte is on the host."""
-    from gpuk_b200 import workloads as oin
+    oin = load_workloads()
     device = torch.device("cuda", torch.cuda.current_device())
     hx = oin.make_partial(cfg, rank, world).pin_memory()
     hr = oin.make_residual(cfg).pin_memory()
@@ -248,12 +367,12 @@ def run_e2e(cfg, env, rank, world, steps, warmup, barrier):
     o_q = torch.empty(hx.shape, dtype=torch.float8_e4m3fn).pin_memory()
     o_s = torch.empty(cfg.tokens, 1, dtype=torch.float32).pin_memory()
     static = torch.tensor([cfg.static_scale], dtype=torch.float32, device=device) if cfg.quant_type == 4 else None
-    chunks = int(os.environ.get("GPUK_E2E_CHUNKS", "4"))
+    chunks = 4
 
     def call(_):
         env.allreduce_add_rms_fused_host(hx, hr, w, cfg.eps, (o_res, o_q, o_s), chunks=chunks, static_scale=static)
 
-    secs = max_over_ranks(time_calls(call, 1, steps, warmup, barrier), world)
+    secs, _ = time_calls(call, 1, steps, warmup, barrier, world)
     h2d = hx.numel() * 2 + hr.numel() * 2
     d2h = o_res.numel() * 2 + o_q.numel() + (o_s.numel() * 4 if static is None else 0)
     return {"value": secs / steps * 1e6, "unit": "us/call", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -278,7 +397,7 @@ def run_model(env, rank, world, steps, warmup, barrier):
         def step(_):
             model.forward(tokens, pos, cache_len=ctx + 1)
 
-        secs = max_over_ranks(time_calls(step, 1, steps, warmup, barrier), world)
+        secs, _ = time_calls(step, 1, steps, warmup, barrier, world, min_seconds=0.0)
         out[f"us_per_step_{name}"] = secs / steps * 1e6
         try:
             g = torch.cuda.CUDAGraph()
@@ -291,7 +410,7 @@ def run_model(env, rank, world, steps, warmup, barrier):
                 with torch.cuda.graph(g, stream=s):
                     step(0)
             torch.cuda.current_stream().wait_stream(s)
-            secs = max_over_ranks(time_calls(lambda i: g.replay(), 1, steps, warmup, barrier), world)
+            secs, _ = time_calls(lambda i: g.replay(), 1, steps, warmup, barrier, world, min_seconds=0.0)
             out[f"us_per_step_{name}_graph"] = secs / steps * 1e6
             del g
         except Exception as e:   # a capture failure is reported, not fatal
@@ -307,78 +426,137 @@ def run_model(env, rank, world, steps, warmup, barrier):
 # ---------------------------------------------------------------------------------------
 # the reference's CPU path on the host cores
 # ---------------------------------------------------------------------------------------
-def _cpu_worker(rank, world, port, cfg_key, steps, warmup, threads, q):
+def _cpu_worker(rank, world, store_path, cfg_key, steps, warmup, threads, q):
+    """One CPU rank of the reference's native path (gpuk/__init__.py:147-173): gloo all_reduce of the bf16
+    partials, then the PyTorch operator sequence.  Touches neither CUDA nor the product package."""
     import torch.distributed as dist
     from oracle import epilogue_oracle as eo
-    from gpuk_b200 import workloads as oin
+    oin = load_workloads()
     torch.set_num_threads(max(1, threads))
     cfg = oin.CONFIGS[cfg_key]
-    if world > 1:
-        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
-    x = oin.make_partial(cfg, rank, world)
-    res = oin.make_residual(cfg)
-    w = oin.make_weight(cfg)
-    times = []
-    for i in range(warmup + steps):
-        xi = x.clone()
+    try:
         if world > 1:
-            dist.barrier()
-        t0 = time.perf_counter()
+            store = dist.FileStore(store_path, world)
+            dist.init_process_group("gloo", store=store, rank=rank, world_size=world)
+        x = oin.make_partial(cfg, rank, world)
+        res = oin.make_residual(cfg)
+        w = oin.make_weight(cfg)
+        times, ar_times = [], []
+        for i in range(warmup + steps):
+            xi = x.clone()
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            if world > 1:
+                dist.all_reduce(xi)                       # gpuk/__init__.py:156
+            t1 = time.perf_counter()
+            eo.add_rms_quant(xi, res, w, cfg.eps, cfg.quant_type, cfg.static_scale)   # :157-164
+            if world > 1:
+                dist.barrier()
+            times.append(time.perf_counter() - t0)
+            ar_times.append(t1 - t0)
+        if rank == 0:
+            q.put(("ok", times[warmup:], ar_times[warmup:]))
         if world > 1:
-            dist.all_reduce(xi)                       # gpuk/__init__.py:156
-        eo.add_rms_quant(xi, res, w, cfg.eps, cfg.quant_type, cfg.static_scale)   # :157-164
-        if world > 1:
-            dist.barrier()
-        times.append(time.perf_counter() - t0)
-    if rank == 0:
-        q.put(times[warmup:])
-    if world > 1:
-        dist.destroy_process_group()
+            dist.destroy_process_group()
+    except Exception as e:   # reported to the parent instead of a silent death
+        if rank == 0:
+            q.put(("error", repr(e)[:300], None))
+        raise
 
 
-def cpu_reference_us(cfg_key, world, steps, warmup):
-    """Median microseconds per call of the reference's CPU path: torch CPU operators, gloo
-    all-reduce among `world` local processes sharing the host cores."""
-    import socket
+_ELASTIC_KEYS = ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE", "GROUP_RANK", "GROUP_WORLD_SIZE", "ROLE_RANK",
+                 "ROLE_WORLD_SIZE", "ROLE_NAME", "MASTER_ADDR", "MASTER_PORT")
+
+
+def cpu_model_name():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.lower().startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except Exception:
+        pass
+    return "unknown"
+
+
+def cpu_reference_us(cfg_key, world, steps, warmup, timeout_s=240):
+    """Median microseconds per call of the reference's CPU path: torch CPU operators, gloo all-reduce among
+    `world` local processes sharing the host cores.  The ranks meet through a FileStore in a temporary
+    directory, and every launcher variable (RANK, MASTER_*, TORCHELASTIC_*) is hidden from them, so it works
+    the same inside and outside torch.distributed.run.  Returns a dict; raises RuntimeError with the reason."""
+    import queue as queue_mod
     import torch.multiprocessing as mp
     cores = os.cpu_count() or 1
     threads = max(1, cores // world)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
-    env_backup = {k: os.environ.pop(k) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT",
-                                                 "TORCHELASTIC_RUN_ID", "GROUP_RANK", "LOCAL_WORLD_SIZE")
-                  if k in os.environ}
+    tmp = tempfile.mkdtemp(prefix="gpuk_cpu_ref_")
+    hidden_env = {k: os.environ.pop(k) for k in list(os.environ)
+                  if k in _ELASTIC_KEYS or k.startswith("TORCHELASTIC") or k.startswith("TORCH_ELASTIC")}
+    hidden_env["CUDA_VISIBLE_DEVICES"] = os.environ.get("CUDA_VISIBLE_DEVICES")
+    os.environ["CUDA_VISIBLE_DEVICES"] = ""      # the CPU arm's processes see no GPU
+    procs = []
     try:
-        procs = [ctx.Process(target=_cpu_worker, args=(r, world, port, cfg_key, steps, warmup, threads, q))
+        procs = [ctx.Process(target=_cpu_worker, args=(r, world, os.path.join(tmp, "store"), cfg_key, steps, warmup, threads, q))
                  for r in range(world)]
         for p in procs:
             p.start()
-        times = q.get(timeout=900)
+        try:
+            status, times, ar_times = q.get(timeout=timeout_s)
+        except queue_mod.Empty:
+            raise RuntimeError(f"CPU ranks did not finish within {timeout_s} s")
+        if status != "ok":
+            raise RuntimeError(f"CPU rank failed: {times}")
         for p in procs:
-            p.join(timeout=120)
+            p.join(timeout=60)
     finally:
-        os.environ.update(env_backup)
-    return statistics.median(times) * 1e6, threads * world, threads
+        for p in procs:
+            if p.is_alive():
+                p.kill()
+        for k, v in hidden_env.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+        shutil.rmtree(tmp, ignore_errors=True)
+    return {"us": statistics.median(times) * 1e6, "allreduce_us": statistics.median(ar_times) * 1e6,
+            "cores": threads * world, "threads_per_rank": threads, "ranks": world, "host_cpus": cores,
+            "cpu_model": cpu_model_name()}
+
+
+def cpu_baseline_object(cfg, r, steps):
+    return {"value": r["us"], "unit": "us/call", "cores": r["cores"], "kind": "port", "ranks": r["ranks"],
+            "threads_per_rank": r["threads_per_rank"], "host_cpus": r["host_cpus"], "cpu_model": r["cpu_model"],
+            "allreduce_only_us": r["allreduce_us"] if r["ranks"] > 1 else None,
+            "sample": f"{steps} calls of the full {cfg.tokens}x{cfg.hidden} workload, {r['ranks']} process(es) x "
+                      f"{r['threads_per_rank']} threads" + (", gloo all_reduce" if r["ranks"] > 1 else ", no exchange at one rank")
+                      + ", median"}
 
 
 def reference_arm(args, rank, world):
+    """The reference's own CPU implementation of the path (PyTorch CPU operators + gloo), timed on the host
+    cores: rank 0 alone runs it, with `world` CPU ranks; the other launcher ranks exit at once."""
     if rank != 0:
         return
-    from gpuk_b200 import workloads as oin
+    oin = load_workloads()
     cfg = oin.CONFIGS[args.workload]
+    if args.workload == "c1":
+        world = 2
     steps = max(1, min(args.steps, 30))
     warmup = max(1, min(args.warmup, 5))
-    us, cores, threads = cpu_reference_us(args.workload, world, steps, warmup)
+    try:
+        r = cpu_reference_us(args.workload, world, steps, warmup)
+    except Exception as e:
+        print(json.dumps({"impl": "reference", "unavailable": f"CPU/gloo reference arm failed: {repr(e)[:200]}"}), flush=True)
+        return
+    us = r["us"]
     line = {
-        "impl": "reference", "metric": "fused_ar_rmsnorm_fp8_us_per_call", "value": us, "unit": "us/call",
+        "impl": "reference", "metric": METRIC, "value": us, "unit": "us/call",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": us * 1e-3, "higher_is_better": False,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": cfg.name, "tokens": cfg.tokens, "hidden": cfg.hidden, "ranks": world,
-                   "backend": "torch CPU operators" + (" + gloo all_reduce" if world > 1 else "")},
-        "cpu_baseline": {"value": us, "unit": "us/call", "cores": cores, "kind": "port",
-                         "sample": f"{steps} calls of the full {cfg.tokens}x{cfg.hidden} workload, "
-                                   f"{world} process(es) x {threads} threads, median"},
+        "config": config_dict(cfg, world),
+        "backend": "torch CPU operators" + (" + gloo all_reduce" if world > 1 else ""),
+        "cpu_baseline": cpu_baseline_object(cfg, r, steps),
         "e2e": {"value": us, "unit": "us/call", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -388,7 +566,7 @@ def reference_arm(args, rank, world):
 def run_crossover(env, gpuk, rank, world, barrier, hidden=8192):
     """Microseconds per call (CUDA graph replay of the rotating buffer sets) of the three exchanges over
     the token counts between decode and prefill; used to place the thresholds between them."""
-    from gpuk_b200 import workloads as oin
+    oin = load_workloads()
     rows = []
     have_sym = getattr(env, "_sym", None) is not None
     for tokens in (1, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192):
@@ -411,8 +589,74 @@ def run_crossover(env, gpuk, rank, world, barrier, hidden=8192):
                 entry[name] = repr(e)[:120]
         rows.append(entry)
     env.set_option("oneshot_max_bytes", 0)
-    env.set_option("sym_min_bytes", int(os.environ.get("GPUK_SYM_MIN_BYTES", "0")))
+    env.set_option("sym_min_bytes", 0)
     return rows
+
+
+# ---------------------------------------------------------------------------------------
+# a short, fixed case of one kernel: the command to put under ncu
+# ---------------------------------------------------------------------------------------
+def run_case(a):
+    """`--case norm_quant`: the one-GPU kernel `--iters` times; `--case emulated`: the N-rank exchange for all
+    ranks inside one launch on this GPU (--mode 1 = one-shot, 2 = two-shot).  Seeded random bf16 inputs; nothing
+    is checked (the tests do that), the point is a short, bounded run."""
+    import ctypes
+    from gpuk_b200 import cabi
+
+    def ptr(t):
+        return ctypes.c_void_p(t.data_ptr())
+
+    torch.cuda.set_device(0)
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    w = (1 + 0.1 * torch.randn(a.hidden, device=dev)).bfloat16()
+    res = torch.randn(a.tokens, a.hidden, device=dev).bfloat16()
+    if a.case == "norm_quant":
+        x = torch.randn(a.tokens, a.hidden, device=dev).bfloat16()
+        res_out = torch.empty_like(x)
+        q = torch.empty(x.shape, dtype=torch.uint8, device=dev)
+        scale = torch.full((max(a.tokens, 1),), 0.05, dtype=torch.float32, device=dev)
+        for _ in range(a.iters):
+            cabi.check(cabi.lib.gpuk_residual_rms_quant(ptr(x), ptr(res), ptr(w), ptr(res_out), ptr(q), ptr(scale), x.numel(),
+                                                        a.hidden, cabi.DTYPE_BF16, 1e-6, a.quant, stream))
+        torch.cuda.synchronize()
+        print("norm_quant", a.tokens, a.hidden, "scale0", float(scale[0]))
+        return
+    n = a.world
+    msg = a.tokens * a.hidden * 2
+    ws = []
+    for r in range(n):
+        h = ctypes.c_void_p()
+        cabi.check(cabi.lib.gpuk_ws_create(0, r, n, max(msg, 1 << 20), 0, ctypes.byref(h)))
+        ws.append(h)
+    flags, data = (ctypes.c_void_p * n)(), (ctypes.c_void_p * n)()
+    for r in range(n):
+        f, d = ctypes.c_void_p(), ctypes.c_void_p()
+        cabi.check(cabi.lib.gpuk_ws_local_pointers(ws[r], ctypes.byref(f), ctypes.byref(d)))
+        flags[r], data[r] = f, d
+    for r in range(n):
+        cabi.check(cabi.lib.gpuk_ws_set_peer_pointers(ws[r], flags, data, n))
+    xs = [torch.randn(a.tokens, a.hidden, device=dev).bfloat16() for _ in range(n)]
+    outs = [(torch.empty_like(xs[0]), torch.empty(xs[0].shape, dtype=torch.uint8, device=dev),
+             torch.full((max(a.tokens, 1),), 0.05, dtype=torch.float32, device=dev)) for _ in range(n)]
+
+    def arr(ts):
+        return (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
+
+    wsa = (ctypes.c_void_p * n)(*[h.value for h in ws])
+    for _ in range(a.iters):
+        cabi.check(cabi.lib.gpuk_emulated_allreduce_rms(
+            wsa, n, arr(xs), ptr(res), ptr(w), arr([o[0] for o in outs]), arr([o[1] for o in outs]),
+            arr([o[2] for o in outs]), xs[0].numel(), a.hidden, cabi.DTYPE_BF16, 1e-6, a.quant, a.mode, stream))
+    torch.cuda.synchronize()
+    st = (ctypes.c_uint32 * 8)()
+    rc = cabi.lib.gpuk_ws_status(ws[0], st)
+    print("emulated", n, a.mode, a.tokens, a.hidden, "status", rc, list(st))
+    for h in ws:
+        cabi.lib.gpuk_ws_destroy(h)
+    if rc:
+        raise SystemExit(1)
 
 
 # ---------------------------------------------------------------------------------------
@@ -422,12 +666,22 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="gpuk_b200", choices=["gpuk_b200", "reference"])
-    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c3", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-model", action="store_true", help="skip the decoder-model step (config 5) in the sweep")
     ap.add_argument("--crossover", action="store_true", help="also time one-shot / two-shot / symmetric over token counts")
+    ap.add_argument("--case", choices=["norm_quant", "emulated"], help="run one short fixed case of a kernel and exit")
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--quant", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=6)
+    ap.add_argument("--world", type=int, default=8)
+    ap.add_argument("--mode", type=int, default=2)
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     args.warmup = max(args.warmup, 3)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -450,7 +704,7 @@ def main():
         dist.init_process_group("gloo", rank=0, world_size=1)
 
     import gpuk_b200 as gpuk
-    from gpuk_b200 import workloads as oin
+    oin = load_workloads()
 
     env = gpuk.GPUKDistEnv(group=None, device_id=local_rank)
 
@@ -464,7 +718,7 @@ def main():
         sampler.start()
     head = run_config(cfg, env, gpuk, rank, world, args.steps, args.warmup, barrier, native=True, graph=True)
     # keep the same kernel running a little longer so the 100 ms clock sampler sees it under load
-    extra = max(0, int(0.4 / max(head["us_per_call"] * 1e-6, 1e-7)) - args.steps)
+    extra = max(0, int(0.4 / max(head["us_per_call"] * 1e-6, 1e-7)) - args.steps * head["blocks"])
     if extra:
         run_config(cfg, env, gpuk, rank, world, min(extra, 200000), 3, barrier)
     clocks = sampler.stop() if rank == 0 else None
@@ -473,13 +727,13 @@ def main():
 
     sweep = []
     if not args.no_sweep:
-        for key in ("c2", "c3", "c4", "c5"):
+        for key in ("c1", "c2", "c3", "c4", "c5"):
             if key == args.workload:
                 continue
             c = oin.CONFIGS[key]
-            k = max(10, min(args.steps, 20000 if c.tokens <= 64 else (300 if c.tokens >= 8192 else 2000)))
+            k = max(10, min(args.steps, 20000 if c.tokens <= 128 else (300 if c.tokens >= 8192 else 2000)))
             sweep.append(run_config(c, env, gpuk, rank, world, k, min(args.warmup, 20), barrier,
-                                    graph=c.tokens <= 64, native=True))
+                                    graph=c.tokens <= 128, native=True))
 
         if not args.no_model:
             try:
@@ -489,11 +743,18 @@ def main():
 
     crossover = run_crossover(env, gpuk, rank, world, barrier) if (args.crossover and world > 1) else None
 
-    cpu = None
+    cpu = cpu_c1 = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        us, cores, threads = cpu_reference_us(args.workload, 1, 12, 3)
-        cpu = {"value": us, "unit": "us/call", "cores": cores, "kind": "port",
-               "sample": f"12 calls of the full {cfg.tokens}x{cfg.hidden} workload (no exchange at one rank), median"}
+        # bounded samples of the reference's CPU path on this box's host cores: the headline workload at one
+        # rank (no exchange, like the GPU number beside it) and config 1, two gloo ranks at 128 x 4096
+        try:
+            cpu = cpu_baseline_object(cfg, cpu_reference_us(args.workload, 1, 12, 3), 12)
+        except Exception as e:
+            cpu = {"value": None, "unit": "us/call", "cores": 0, "kind": "port", "sample": f"failed: {repr(e)[:160]}"}
+        try:
+            cpu_c1 = cpu_baseline_object(oin.CONFIGS["c1"], cpu_reference_us("c1", 2, 30, 5), 30)
+        except Exception as e:
+            cpu_c1 = {"value": None, "sample": f"failed: {repr(e)[:160]}"}
 
     if rank == 0:
         us = head["us_per_call"]
@@ -501,29 +762,33 @@ def main():
         if world == 1:
             ach = hbm_bytes(cfg.tokens, cfg.hidden) / (us * 1e-6) / 1e9
             roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "traffic": K1_DRAM_TRAFFIC_BYTES_PER_TOKEN_H8192 * cfg.tokens if cfg.hidden == 8192 else None,
+                    "traffic": dram_traffic("norm_quant", cfg.tokens, cfg.hidden),
                     "peak_kind": f"of {peak_kind}",
                     "algorithmic_bytes_per_launch": hbm_bytes(cfg.tokens, cfg.hidden),
-                    "kernel": "fused_norm_quant_kernel"}
+                    "kernel": "fused_norm_quant (one GPU, no exchange)"}
         else:
             ach = bus_bytes(cfg.tokens, cfg.hidden, world) / (us * 1e-6) / 1e9
-            roof = {"bound": "nvlink", "achieved": ach, "peak": NVLINK_PEER_COPY_GBS, "unit": "GB/s",
-                    "frac": ach / NVLINK_PEER_COPY_GBS, "traffic": None,
-                    "peak_kind": "of measured peer copy per direction (nominal 900)",
-                    "frac_of_sm_store_peak": ach / NVLINK_SM_STORE_GBS,
+            roof = {"bound": "nvlink", "achieved": ach, "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s",
+                    "frac": ach / NVLINK_NOMINAL_GBS,
+                    "traffic": dram_traffic(f"two_shot_emulated_{world}", cfg.tokens, cfg.hidden),
+                    "peak_kind": "of nominal NVLink 5 per direction per GPU",
+                    "frac_of_measured_peer_copy_770": ach / NVLINK_PEER_COPY_GBS,
+                    "frac_of_measured_sm_store_690": ach / NVLINK_SM_STORE_GBS,
                     "algorithmic_bytes_per_launch": bus_bytes(cfg.tokens, cfg.hidden, world),
                     "kernel": "ar_kernel (two-shot, fused epilogue)"}
         line = {
-            "metric": "fused_ar_rmsnorm_fp8_us_per_call", "value": us, "unit": "us/call", "n_gpus": world,
+            "metric": METRIC, "value": us, "unit": "us/call", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": us * 1e-3, "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": cfg.name, "tokens": cfg.tokens, "hidden": cfg.hidden, "ranks": world,
-                       "quant": "per-token dynamic e4m3fn /448", "l2": f"rotating {head['buffer_sets']} buffer sets (> 4x L2)"},
+            "config": config_dict(cfg, world),
+            "l2": f"rotating {head['buffer_sets']} buffer sets (> 4x L2)",
+            "timed": f"median of {head['blocks']} blocks of {args.steps} calls, max over ranks per block",
+            "parity": head["parity"],
             "busbw_gbs": roof["achieved"] if world > 1 else None,
             "roofline": roof, "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
             "nccl_unfused_us_per_call": head.get("us_per_call_nccl_unfused"),
             "us_per_call_graph": head.get("us_per_call_graph"),
-            "cpu_baseline": cpu, "sweep": sweep,
+            "cpu_baseline": cpu, "cpu_baseline_c1_gloo2": cpu_c1, "sweep": sweep,
         }
         if crossover is not None:
             line["crossover"] = crossover

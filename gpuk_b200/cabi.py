@@ -13,7 +13,8 @@ from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_uint8, c_uint32
 HERE = os.path.dirname(os.path.abspath(__file__))
 CORE_LIB = os.path.join(HERE, "libgpuk_core.so")
 
-OK, ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOT_READY, ERR_TOO_LARGE, ERR_PEER_TIMEOUT = range(7)
+(OK, ERR_INVALID_ARGUMENT, ERR_CUDA, ERR_UNSUPPORTED, ERR_NOT_READY, ERR_TOO_LARGE, ERR_PEER_TIMEOUT,
+ ERR_BAD_LAUNCH) = range(8)
 DTYPE_BF16, DTYPE_F16, DTYPE_F32 = 0, 1, 2
 QUANT_NONE, QUANT_FP8_E4M3FN_240, QUANT_FP8_E4M3FNUZ_120, QUANT_FP8_E4M3FN_448, QUANT_FP8_E4M3FN_448_STATIC = range(5)
 IPC_HANDLE_BYTES = 64
@@ -24,7 +25,8 @@ SYM_FLAG_BYTES = 2 * 2048 * 8 * 8   # tail of a symmetric buffer that holds the 
 class Plan(ctypes.Structure):
     _fields_ = [("one_shot", c_int), ("vpt", c_int), ("threads", c_int), ("rows_per_chunk", c_int),
                 ("grid", c_int), ("rows", c_int), ("row_vecs", c_int), ("message_bytes", c_int64),
-                ("cluster", c_int), ("lead_push", c_int), ("lead_reduce", c_int)]
+                ("cluster", c_int), ("lead_push", c_int), ("lead_reduce", c_int),
+                ("ws", c_int), ("ws_grid", c_int), ("ws_vpt", c_int), ("ws_tf", c_int), ("ws_tr", c_int), ("ws_ts", c_int)]
 
 
 class GpukError(RuntimeError):
@@ -64,6 +66,7 @@ _SIGNATURES = {
     "gpuk_plan_allreduce_rms": (c_int, [c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, POINTER(Plan)]),
     "gpuk_ws_set_oneshot_max_bytes": (c_int, [_P, c_int64]),
     "gpuk_ws_set_option": (c_int, [_P, c_char_p, c_int64]),
+    "gpuk_set_tuning": (c_int, [c_char_p, c_int64]),
     "gpuk_ws_set_timeout_ns": (c_int, [_P, c_uint64]),
     "gpuk_ws_status": (c_int, [_P, POINTER(c_uint32)]),
     "gpuk_ws_clear_status": (c_int, [_P]),
@@ -72,6 +75,7 @@ _SIGNATURES = {
                                             POINTER(_P), c_int64, c_int, c_int, c_float, c_int, c_int, _P]),
     "gpuk_selfcheck_allreduce_rms": (c_int, [c_int, POINTER(_P), _P, _P, POINTER(_P), POINTER(_P), POINTER(_P),
                                              c_int64, c_int, c_int, c_float, c_int, c_int, _P]),
+    "gpuk_selfcheck_status": (c_int, [POINTER(c_uint32), _P]),
 }
 for _name, (_res, _args) in _SIGNATURES.items():
     _fn = getattr(lib, _name)

@@ -27,7 +27,16 @@ struct Quant {
     int mode;        // QuantMode
     int fnuz;        // 1: e4m3fnuz bit patterns (bias 8, no negative zero), 0: e4m3fn
     float fp8_max;   // saturation value used for the scale and the clamp (240 / 120 / 448)
+    float inv_fp8_max;   // its correctly rounded reciprocal
 };
+__host__ __device__ inline Quant make_quant(int mode, int fnuz, float fp8_max) {
+    Quant q;
+    q.mode = mode;
+    q.fnuz = fnuz;
+    q.fp8_max = fp8_max;
+    q.inv_fp8_max = fp8_max > 0.f ? static_cast<float>(1.0 / static_cast<double>(fp8_max)) : 0.f;
+    return q;
+}
 
 // ---------------------------------------------------------------------------------------
 // device-resident state of one rank's workspace (local, never mapped by peers)
@@ -44,7 +53,9 @@ struct LocalState {
 // stage codes in status[3]
 enum Stage : int { kStageOneShot = 0, kStageScatter = 1, kStageGather = 2, kStageSelfTest = 3, kStageSymIn = 4, kStageSymOut = 5 };
 
-enum StatusCode : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusSpinCap = 2 };
+// kStatusClusterMismatch: the kernel found itself in a thread-block cluster of another size than the
+// host planned (status[6] = the size seen); it returns before it takes a ticket or writes anything.
+enum StatusCode : uint32_t { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusSpinCap = 2, kStatusClusterMismatch = 3 };
 
 // ---------------------------------------------------------------------------------------
 // 16-byte global memory access
@@ -60,6 +71,47 @@ __device__ __forceinline__ void st_stream(void *p, const uint4 &v) { __stcs(rein
 __device__ __forceinline__ void st_peer(void *p, const uint4 &v) { *reinterpret_cast<uint4 *>(p) = v; }
 
 // ---------------------------------------------------------------------------------------
+// packed fp32 pairs: sm_100 multiplies and fuses two fp32 lanes held in one 64-bit register
+// pair with ONE instruction (mul / add / fma .f32x2, each lane rounded like the scalar form),
+// which halves the issue slots of the per-element arithmetic.  .x is the low lane.
+// ---------------------------------------------------------------------------------------
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 f2_make(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_make_bits(uint32_t lo, uint32_t hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_splat(float v) { return f2_make(v, v); }
+__device__ __forceinline__ void f2_split(f32x2 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ float f2_sum(f32x2 v) {
+    float lo, hi;
+    f2_split(v, lo, hi);
+    return lo + hi;
+}
+
+// ---------------------------------------------------------------------------------------
 // element traits: how 16 bytes unpack to fp32 lanes and round back
 // ---------------------------------------------------------------------------------------
 template <typename T>
@@ -68,6 +120,27 @@ struct Elem;
 template <>
 struct Elem<__nv_bfloat16> {
     static constexpr int kVec = 8;
+    static constexpr int kPairs = 4;
+    // the 16 bytes as four fp32 pairs (elements 2k, 2k+1), and back with one rounding per element
+    __device__ static __forceinline__ void unpack2(const uint4 &u, f32x2 (&p)[4]) {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = f2_make_bits(w[i] << 16, w[i] & 0xffff0000u);
+    }
+    __device__ static __forceinline__ uint4 pack2(const f32x2 (&p)[4]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            f2_split(p[i], lo, hi);
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(hi), "f"(lo));
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // sign bits of elements 4h .. 4h+3 at bits 7, 15, 23, 31
+    __device__ static __forceinline__ uint32_t sign_bytes(const uint4 &u, int h) {
+        return __byte_perm(h ? u.z : u.x, h ? u.w : u.y, 0x7531) & 0x80808080u;
+    }
     __device__ static __forceinline__ void unpack(const uint4 &u, float (&f)[8]) {
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -133,6 +206,29 @@ struct Elem<__nv_bfloat16> {
 template <>
 struct Elem<__half> {
     static constexpr int kVec = 8;
+    static constexpr int kPairs = 4;
+    __device__ static __forceinline__ void unpack2(const uint4 &u, f32x2 (&p)[4]) {
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            p[i] = f2_make(v.x, v.y);
+        }
+    }
+    __device__ static __forceinline__ uint4 pack2(const f32x2 (&p)[4]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            f2_split(p[i], lo, hi);
+            __half2 h = __floats2half2_rn(lo, hi);
+            w[i] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ static __forceinline__ uint32_t sign_bytes(const uint4 &u, int h) {
+        return __byte_perm(h ? u.z : u.x, h ? u.w : u.y, 0x7531) & 0x80808080u;
+    }
     __device__ static __forceinline__ void unpack(const uint4 &u, float (&f)[8]) {
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -192,6 +288,20 @@ struct Elem<__half> {
 template <>
 struct Elem<float> {
     static constexpr int kVec = 4;
+    static constexpr int kPairs = 2;
+    __device__ static __forceinline__ void unpack2(const uint4 &u, f32x2 (&p)[2]) {
+        p[0] = f2_make_bits(u.x, u.y);
+        p[1] = f2_make_bits(u.z, u.w);
+    }
+    __device__ static __forceinline__ uint4 pack2(const f32x2 (&p)[2]) {
+        float a, b, c, d;
+        f2_split(p[0], a, b);
+        f2_split(p[1], c, d);
+        return make_uint4(__float_as_uint(a), __float_as_uint(b), __float_as_uint(c), __float_as_uint(d));
+    }
+    __device__ static __forceinline__ uint32_t sign_bytes(const uint4 &u, int) {
+        return __byte_perm(__byte_perm(u.x, u.y, 0x7773), __byte_perm(u.z, u.w, 0x7773), 0x5410) & 0x80808080u;
+    }
     __device__ static __forceinline__ void unpack(const uint4 &u, float (&f)[4]) {
         f[0] = __uint_as_float(u.x);
         f[1] = __uint_as_float(u.y);
@@ -237,15 +347,26 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+// A group of warps that reduces together: the whole CTA (bar 0), or one role of a kernel whose
+// warps are specialised (its own named barrier).  `n` is a multiple of 32.
+struct Group {
+    int tid;   // this thread's index inside the group
+    int n;     // threads in the group
+    int bar;   // hardware barrier the group synchronises on
+};
+__device__ __forceinline__ Group whole_cta() { return Group{static_cast<int>(threadIdx.x), static_cast<int>(blockDim.x), 0}; }
+__device__ __forceinline__ void group_sync(const Group &g) {
+    asm volatile("bar.sync %0, %1;" ::"r"(g.bar), "r"(g.n) : "memory");
+}
 // After the barrier every thread reads all per-warp partials with broadcast 16-byte loads and
 // combines them in warp order (same order in every thread, so the result is uniform).
-__device__ __forceinline__ float block_sum(float v, float *sm) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+__device__ __forceinline__ float block_sum(float v, float *sm, const Group &g) {
+    const int lane = g.tid & 31, warp = g.tid >> 5, nwarps = g.n >> 5;
     v = warp_sum(v);
     if (nwarps == 1) return v;
     if (lane == 0) sm[warp] = v;
     if (warp == 0 && lane >= nwarps) sm[lane] = 0.f;   // pad to a multiple of four
-    __syncthreads();
+    group_sync(g);
     float acc = 0.f;
     for (int i = 0; i < nwarps; i += 4) {
         const float4 q = *reinterpret_cast<const float4 *>(sm + i);
@@ -253,13 +374,13 @@ __device__ __forceinline__ float block_sum(float v, float *sm) {
     }
     return acc;
 }
-__device__ __forceinline__ float block_max(float v, float *sm) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+__device__ __forceinline__ float block_max(float v, float *sm, const Group &g) {
+    const int lane = g.tid & 31, warp = g.tid >> 5, nwarps = g.n >> 5;
     v = warp_max(v);
     if (nwarps == 1) return v;
     if (lane == 0) sm[warp] = v;
     if (warp == 0 && lane >= nwarps) sm[lane] = 0.f;   // operands are magnitudes, so 0 is the identity
-    __syncthreads();
+    group_sync(g);
     float acc = 0.f;
     for (int i = 0; i < nwarps; i += 4) {
         const float4 q = *reinterpret_cast<const float4 *>(sm + i);
@@ -344,7 +465,7 @@ __device__ __forceinline__ void st_cluster_f32(float *local, int cta, float v) {
 template <bool MAX>
 __device__ __forceinline__ float cluster_combine(float v, float *slots, int cl_rank, int cl_size) {
     if (cl_size == 1) return v;
-    if (threadIdx.x < cl_size) st_cluster_f32(slots + cl_rank, threadIdx.x, v);
+    if (threadIdx.x < cl_size) st_cluster_f32(slots + cl_rank, threadIdx.x, v);   // clusters only occur with whole-CTA groups
     cluster_barrier();
     float acc = slots[0];
     for (int i = 1; i < cl_size; ++i) acc = MAX ? fmaxf(acc, slots[i]) : acc + slots[i];
@@ -358,6 +479,22 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
     uint16_t r;
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
     return r;
+}
+// Two fp32 pairs (elements e, e+1 and e+2, e+3) -> four FP8 e4m3fn bytes in element order.
+__device__ __forceinline__ uint32_t cvt_e4m3x4_pairs(f32x2 a, f32x2 b) {
+    uint32_t w;
+    asm("{\n\t.reg .b16 lo, hi;\n\t.reg .f32 a0, a1, b0, b1;\n\t"
+        "mov.b64 {a0, a1}, %1;\n\tmov.b64 {b0, b1}, %2;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, a1, a0;\n\tcvt.rn.satfinite.e4m3x2.f32 hi, b1, b0;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(w) : "l"(a), "l"(b));
+    return w;
+}
+// A byte equal to 0x80 (negative zero in e4m3fn, NaN in e4m3fnuz) becomes 0x00; others unchanged.
+__device__ __forceinline__ uint32_t fold_negative_zero_bytes(uint32_t w) {
+    const uint32_t low7 = w & 0x7f7f7f7fu;
+    const uint32_t nonzero7 = (low7 + 0x7f7f7f7fu) & 0x80808080u;   // bit 7 set where low 7 bits != 0
+    return low7 | (w & nonzero7);
 }
 // Four floats -> four FP8 bytes (little-endian lane order).  For the fnuz flavour the value
 // is doubled (e4m3fnuz has exponent bias 8 where e4m3fn has 7, so code_fnuz(x) == code_fn(2x))

@@ -62,9 +62,12 @@ int gpuk::set_last_error(int code, const char *fmt, ...) {
 
 cudaError_t gpuk::launch_kernel(const void *fn, int grid, int threads, int cluster, bool all_resident, void **args,
                                 cudaStream_t stream, size_t dynamic_smem) {
-    static const bool pdl = [] { const char *e = getenv("GPUK_PDL"); return !e || atoi(e) != 0; }();
+    // A grid that must be resident as a whole is launched cooperatively, which the driver refuses
+    // when it does not fit.  The cooperative attribute is never combined with a cluster dimension
+    // (the combination is not honoured everywhere: a launch can be accepted and run without its
+    // cluster): a clustered all-resident launch carries the cluster attribute alone, its callers
+    // size the grid in whole clusters with resident_ctas(), and every wait in the kernels is bounded.
     if (cluster <= 1 && all_resident) return cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(threads), args, dynamic_smem, stream);
-    if (cluster <= 1 && !pdl) return cudaLaunchKernel(fn, dim3(grid), dim3(threads), args, dynamic_smem, stream);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(threads);
@@ -79,27 +82,14 @@ cudaError_t gpuk::launch_kernel(const void *fn, int grid, int threads, int clust
         attrs[n].val.clusterDim.z = 1;
         ++n;
     }
-    if (all_resident) {
-        attrs[n].id = cudaLaunchAttributeCooperative;
-        attrs[n].val.cooperative = 1;
-        ++n;
-    } else if (pdl) {
+    if (!all_resident) {
         attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attrs[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
     cfg.attrs = attrs;
     cfg.numAttrs = n;
-    cudaError_t e = cudaLaunchKernelExC(&cfg, fn, args);
-    if (e != cudaSuccess && all_resident && cluster > 1 && e != cudaErrorCooperativeLaunchTooLarge) {
-        // The cooperative attribute was not accepted together with a cluster.  The callers of
-        // all_resident launches size the grid with resident_ctas() and every wait in the kernels
-        // is bounded, so the launch goes ahead without it.
-        cudaGetLastError();
-        cfg.numAttrs = 1;
-        e = cudaLaunchKernelExC(&cfg, fn, args);
-    }
-    return e;
+    return cudaLaunchKernelExC(&cfg, fn, args);
 }
 
 cudaError_t gpuk::resident_ctas(const void *fn, int threads, int cluster, int sm_count, int64_t *ctas) {
@@ -142,9 +132,24 @@ constexpr uint64_t kDefaultTimeoutNs = 2000000000ull;
 constexpr size_t kFlagBytes = 4096;             // the allocation behind the "barrier handle"
 constexpr int64_t kTailBytes = 256;             // never written by an exchange
 constexpr int kPlainRowVecs = 1024;             // the plain all-reduce views its input as 16 KiB rows
-constexpr int kDefaultK1Stages = 3;             // shared-memory stages of the one-GPU kernel for many rows (0: off)
-constexpr int kK1StagedMinRowsPerSm = 16;       // ... used from this many rows per SM (measured: 0.94 vs 0.89 of HBM peak
-                                                // at 110 rows per SM, no gain at 7 rows per SM)
+// The one-GPU kernel for many rows (persistent CTAs, rows staged through shared memory).  Measured on
+// B200 at hidden 8192, fraction of the HBM copy peak, one row per CTA / staged with 512 threads and two
+// stages: 1024 rows 0.70 / 0.63, 2048 rows 0.84 / 0.82, 4096 rows 0.89 / 0.93, 16384 x 7168 0.97 / 0.98.
+constexpr int kDefaultK1Threads = 512;          // preferred CTA size of that kernel
+constexpr int kDefaultK1Stages = 2;             // its shared-memory stages (0: never use it)
+constexpr int64_t kK1StagedMinRows(int sms) { return 20ll * sms; }   // ... used from this many rows
+
+// process-wide tuning of the one-GPU kernel (gpuk_set_tuning); negative / zero: built-in choice
+struct Tuning {
+    int k1_stages = -1;
+    int64_t k1_staged_min_rows = -1;
+    int k1_ctas_per_sm = 0;
+    int k1_threads = 0;       // preferred CTA size of the persistent variant
+};
+Tuning g_tuning;
+constexpr int kWsFinishThreads = 512;           // warp-specialised two-shot kernel: threads per role (kernels.cuh: kWsMaxThreads)
+constexpr int kWsReduceThreads = 128;
+constexpr int kWsScatterThreads = 128;
 constexpr int kDefaultLeadPush = 1;             // two-shot pipeline depths (chunks), see ar_body
 constexpr int kDefaultLeadReduce = 1;
 
@@ -170,16 +175,18 @@ int64_t default_oneshot_max_bytes(int world) {
     }
 }
 
-bool quant_from_type(int quant_type, Quant *q) {
+}  // namespace
+bool gpuk::quant_from_type(int quant_type, Quant *q) {
     switch (quant_type) {
-    case GPUK_QUANT_NONE: *q = {kQuantNone, 0, 0.f}; return true;
-    case GPUK_QUANT_FP8_E4M3FN_240: *q = {kQuantDynamic, 0, 240.f}; return true;
-    case GPUK_QUANT_FP8_E4M3FNUZ_120: *q = {kQuantDynamic, 1, 120.f}; return true;
-    case GPUK_QUANT_FP8_E4M3FN_448: *q = {kQuantDynamic, 0, 448.f}; return true;
-    case GPUK_QUANT_FP8_E4M3FN_448_STATIC: *q = {kQuantStatic, 0, 448.f}; return true;
+    case GPUK_QUANT_NONE: *q = make_quant(kQuantNone, 0, 0.f); return true;
+    case GPUK_QUANT_FP8_E4M3FN_240: *q = make_quant(kQuantDynamic, 0, 240.f); return true;
+    case GPUK_QUANT_FP8_E4M3FNUZ_120: *q = make_quant(kQuantDynamic, 1, 120.f); return true;
+    case GPUK_QUANT_FP8_E4M3FN_448: *q = make_quant(kQuantDynamic, 0, 448.f); return true;
+    case GPUK_QUANT_FP8_E4M3FN_448_STATIC: *q = make_quant(kQuantStatic, 0, 448.f); return true;
     default: return false;
     }
 }
+namespace {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -187,10 +194,7 @@ int max_threads_for(int vpt) { return vpt == 4 ? 256 : (vpt == 8 ? 512 : 1024); 
 
 // Tile of a row: `vpt` 16-byte vectors per thread, `threads` per CTA.
 bool pick_tile(int row_vecs, bool latency, int *vpt, int *threads) {
-    int target = latency ? 1024 : 256;
-    // tuning knob for experiments: preferred CTA size of the bandwidth tile
-    static const int forced = [] { const char *e = getenv("GPUK_TILE_THREADS"); return e ? atoi(e) : 0; }();
-    if (!latency && forced >= 32 && forced <= 1024) target = forced;
+    const int target = latency ? 1024 : 256;
     int v = 1;
     while (v < 8 && row_vecs > v * target) v *= 2;
     while ((row_vecs + v - 1) / v > max_threads_for(v)) {
@@ -233,8 +237,11 @@ struct gpuk_ws {
     bool have_data = false, have_flags = false;
     std::vector<void *> ipc_opened;
     int64_t oneshot_max_bytes = 0;
-    int opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default / environment
+    int opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default
     int opt_lead_push = 0, opt_lead_reduce = 0;
+    int opt_cluster = 0;                 // CTAs per row (0: the planner decides)
+    int opt_two_shot_ws = 1;             // 1: two-shot calls without clusters run the warp-specialised kernel
+    bool test_withhold_cluster = false;  // test hook: launch without the planned cluster attribute
     // exchange through symmetric memory (gpuk_ws_attach_symmetric)
     char *sym[kMaxRanks] = {};
     char *sym_mc = nullptr;
@@ -257,6 +264,7 @@ const char *gpuk_status_string(int status) {
     case GPUK_ERR_NOT_READY: return "peer memory not opened";
     case GPUK_ERR_TOO_LARGE: return "message larger than the workspace";
     case GPUK_ERR_PEER_TIMEOUT: return "timed out waiting for a peer";
+    case GPUK_ERR_BAD_LAUNCH: return "kernel ran in another launch shape than planned";
     default: return "unknown status";
     }
 }
@@ -264,17 +272,24 @@ const char *gpuk_status_string(int status) {
 // ---------------------------------------------------------------------------------------
 // planning (pure host arithmetic)
 // ---------------------------------------------------------------------------------------
+// Per-workspace overrides of the planner's choices (gpuk_ws_set_option); 0 = the planner decides.
+struct PlanOverrides {
+    int cluster = 0;          // CTAs per row: 1, 2, 4 or 8
+    int rows_per_chunk = 0;
+    bool allow_cluster = true;   // false: every row stays in one CTA (the exchange through symmetric memory)
+    bool allow_ws = true;        // false: never the warp-specialised two-shot kernel
+};
+
 static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int sm_count, int ctas_per_sm_limit,
-                     int64_t oneshot_max_bytes, bool allow_cluster, gpuk_plan *out);
+                     int64_t oneshot_max_bytes, const PlanOverrides &ov, gpuk_plan *out);
 
 int gpuk_plan_allreduce_rms(int world_size, int64_t numel, int hidden, int dtype, int sm_count,
                             int ctas_per_sm_limit, int64_t oneshot_max_bytes, gpuk_plan *out) {
-    return plan_call(world_size, numel, hidden, dtype, sm_count, ctas_per_sm_limit, oneshot_max_bytes, true, out);
+    return plan_call(world_size, numel, hidden, dtype, sm_count, ctas_per_sm_limit, oneshot_max_bytes, PlanOverrides(), out);
 }
 
-// allow_cluster = false: every row stays in one CTA (the exchange through symmetric memory)
 static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int sm_count, int ctas_per_sm_limit,
-                     int64_t oneshot_max_bytes, bool allow_cluster, gpuk_plan *out) {
+                     int64_t oneshot_max_bytes, const PlanOverrides &ov, gpuk_plan *out) {
     if (!out) return fail(GPUK_ERR_INVALID_ARGUMENT, "plan: out is null");
     const int es = elem_size(dtype);
     if (!es) return fail(GPUK_ERR_UNSUPPORTED, "plan: unknown dtype %d", dtype);
@@ -305,10 +320,9 @@ static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int s
     // Few rows: a row is split over the CTAs of a thread-block cluster so that the exchange runs on
     // many SMs, as long as a CTA keeps at least 128 vectors.
     int cluster = 1;
-    if (world_size > 1 && fused && allow_cluster) {
+    if (world_size > 1 && fused && ov.allow_cluster) {
         while (cluster < 8 && (row_vecs + 2 * cluster - 1) / (2 * cluster) >= 128 && rows * 2 * cluster <= 2ll * sm_count) cluster *= 2;
-        static const int env_cluster = [] { const char *e = getenv("GPUK_CLUSTER"); return e ? atoi(e) : 0; }();
-        if (env_cluster == 1 || env_cluster == 2 || env_cluster == 4 || env_cluster == 8) cluster = env_cluster;
+        if (ov.cluster == 1 || ov.cluster == 2 || ov.cluster == 4 || ov.cluster == 8) cluster = ov.cluster;
         while (cluster > 1 && (row_vecs + cluster - 1) / cluster < 32) cluster /= 2;
     }
     const int seg_vecs = (row_vecs + cluster - 1) / cluster;
@@ -322,27 +336,37 @@ static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int s
         if (!fused) { vpt = 4; threads = std::max(32, ((row_vecs + 3) / 4 + 31) / 32 * 32); }
     }
     int per_sm = std::max(1, std::min(4, 1024 / threads));
-    // tuning knobs for experiments (read once): CTAs per SM and rows per pipeline chunk
-    static const int env_per_sm = [] { const char *e = getenv("GPUK_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
-    static const int env_rpc = [] { const char *e = getenv("GPUK_ROWS_PER_CHUNK"); return e ? atoi(e) : 0; }();
-    if (env_per_sm > 0) per_sm = std::min(per_sm, env_per_sm);
     if (ctas_per_sm_limit > 0) per_sm = std::min(per_sm, ctas_per_sm_limit);
     const int64_t cta_cap = std::min<int64_t>(static_cast<int64_t>(sm_count) * per_sm, kMaxBlocks);
     int rpc = 1;
     if (world_size > 1 && !one_shot) {
         const int vpr = (row_vecs + world_size - 1) / world_size;
         if (rows > cta_cap) rpc = std::max(1, std::min(4, (threads + vpr - 1) / vpr));
-        if (env_rpc > 0) rpc = std::min(env_rpc, 64);
+        if (ov.rows_per_chunk > 0) rpc = std::min(ov.rows_per_chunk, 64);
     }
     const int64_t nchunks = (rows + rpc - 1) / rpc;
     int64_t grid;
     if (world_size == 1) grid = std::min<int64_t>(rows, static_cast<int64_t>(sm_count) * 8);
     else grid = std::min<int64_t>(nchunks, cta_cap / cluster) * cluster;
-    static const int env_lp = [] { const char *e = getenv("GPUK_LEAD_PUSH"); return e ? atoi(e) : 0; }();
-    static const int env_lr = [] { const char *e = getenv("GPUK_LEAD_REDUCE"); return e ? atoi(e) : 0; }();
+    // two-shot without clusters: the warp-specialised kernel, one CTA per SM
+    out->ws = 0;
+    out->ws_vpt = out->ws_tf = out->ws_tr = out->ws_ts = out->ws_grid = 0;
+    if (world_size > 1 && !one_shot && cluster == 1 && ov.allow_ws) {
+        int wv = fused ? 1 : 2;   // the plain all-reduce is built for the 2-vector tile only
+        while (wv < 8 && (row_vecs + wv - 1) / wv > kWsFinishThreads) wv *= 2;
+        const int tf = ((row_vecs + wv - 1) / wv + 31) / 32 * 32;
+        if (tf <= kWsFinishThreads) {
+            out->ws = 1;
+            out->ws_vpt = wv;
+            out->ws_tf = tf;
+            out->ws_tr = kWsReduceThreads;
+            out->ws_ts = kWsScatterThreads;
+            out->ws_grid = static_cast<int>(std::min<int64_t>(rows, sm_count));
+        }
+    }
     out->cluster = cluster;
-    out->lead_push = env_lp > 0 ? std::min(env_lp, 1 << 20) : kDefaultLeadPush;
-    out->lead_reduce = env_lr > 0 ? std::min(env_lr, 1 << 20) : kDefaultLeadReduce;
+    out->lead_push = kDefaultLeadPush;
+    out->lead_reduce = kDefaultLeadReduce;
     out->one_shot = one_shot ? 1 : 0;
     out->vpt = vpt;
     out->threads = threads;
@@ -496,10 +520,6 @@ int gpuk_ws_attach_symmetric(gpuk_ws *ws, void *const *bases, int n, void *mc_ba
     ws->sym_mc = static_cast<char *>(mc_base);
     ws->sym_cap = (bytes - kSymFlagBytes) / 2 / 256 * 256;
     ws->sym_flag_off = 2 * ws->sym_cap;
-    static const int64_t env_min = [] { const char *e = getenv("GPUK_SYM_MIN_BYTES"); return e ? atoll(e) : 0ll; }();
-    if (env_min > 0) ws->sym_min_bytes = env_min;
-    static const int env_mc = [] { const char *e = getenv("GPUK_SYM_MULTICAST"); return e ? atoi(e) : 1; }();
-    ws->sym_use_mc = env_mc != 0;
     return GPUK_OK;
 }
 
@@ -599,6 +619,14 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     } else if (n == "lead_push" || n == "lead_reduce") {
         if (value < 0 || value > (1 << 20)) return fail(GPUK_ERR_INVALID_ARGUMENT, "%s must be in [0, 2^20]", name);
         (n == "lead_push" ? ws->opt_lead_push : ws->opt_lead_reduce) = static_cast<int>(value);
+    } else if (n == "cluster") {
+        if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return fail(GPUK_ERR_INVALID_ARGUMENT, "cluster must be 0, 1, 2, 4 or 8");
+        ws->opt_cluster = static_cast<int>(value);
+    } else if (n == "two_shot_ws") {
+        if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "two_shot_ws must be 0 or 1");
+        ws->opt_two_shot_ws = static_cast<int>(value);
+    } else if (n == "test_withhold_cluster") {
+        ws->test_withhold_cluster = value != 0;
     } else if (n == "sym_multicast") {
         if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "sym_multicast must be 0 or 1");
         ws->sym_use_mc = value != 0;
@@ -626,6 +654,9 @@ int gpuk_ws_status(gpuk_ws *ws, uint32_t out[8]) {
     LocalState host;
     GPUK_CUDA(cudaMemcpy(&host, ws->st, sizeof(host), cudaMemcpyDeviceToHost));
     memcpy(out, host.status, sizeof(host.status));
+    if (out[0] == kStatusClusterMismatch)
+        return fail(GPUK_ERR_BAD_LAUNCH, "rank %u CTA %u ran in a thread-block cluster of %u CTAs, not the planned size; nothing was written",
+                    out[1], out[2], out[6]);
     if (out[0] != 0)
         return fail(GPUK_ERR_PEER_TIMEOUT, "rank %u CTA %u thread %u gave up waiting for data from rank %u in stage %u (word seen 0x%08x)",
                     out[1], out[2], out[5], out[4], out[3], out[6]);
@@ -697,6 +728,8 @@ void fill_epilogue(const CallArgs &a, const Quant &q, int row_vecs, EpilogueArgs
     ep->hidden = a.hidden;
     ep->row_vecs = row_vecs;
     ep->eps = a.eps;
+    ep->hidden_f = static_cast<float>(a.hidden);
+    ep->inv_hidden = static_cast<float>(1.0 / static_cast<double>(a.hidden));
     ep->q = q;
 }
 
@@ -704,7 +737,7 @@ void fill_epilogue(const CallArgs &a, const Quant &q, int row_vecs, EpilogueArgs
 int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated, ArParams *p, ArShape *shape) {
     if (!ws->have_data || !ws->have_flags) return fail(GPUK_ERR_NOT_READY, "peer handles have not been opened");
     const bool fused = a.hidden > 0;
-    Quant q = {kQuantNone, 0, 0.f};
+    Quant q = make_quant(kQuantNone, 0, 0.f);
     if (fused) {
         int rc = check_fused_args(a, &q);
         if (rc) return rc;
@@ -713,7 +746,10 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         if (!aligned16(a.in)) return fail(GPUK_ERR_INVALID_ARGUMENT, "tensor pointers must be 16-byte aligned");
     }
     gpuk_plan plan;
-    int rc = gpuk_plan_allreduce_rms(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, ws->oneshot_max_bytes, &plan);
+    PlanOverrides ov;
+    ov.cluster = ws->opt_cluster;
+    ov.allow_ws = ws->opt_two_shot_ws != 0;
+    int rc = plan_call(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, ws->oneshot_max_bytes, ov, &plan);
     if (rc) return rc;
     if (plan.message_bytes > ws->cap)
         return fail(GPUK_ERR_TOO_LARGE, "message of %lld bytes exceeds the workspace (%lld bytes)",
@@ -730,7 +766,8 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
                         (long long)plan.message_bytes, (long long)ws->sym_cap);
         sym = (ws->sym_mc && ws->sym_use_mc && !emulated) ? 2 : 1;
         force_mode = GPUK_MODE_TWO_SHOT;
-        rc = plan_call(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, 1, false, &plan);
+        ov.allow_cluster = false;
+        rc = plan_call(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, 1, ov, &plan);
         if (rc) return rc;
         one_shot = false;
     }
@@ -743,12 +780,12 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     }
     if (one_shot != (plan.one_shot != 0)) {
         // re-plan with the crossover forced to the requested side
-        rc = gpuk_plan_allreduce_rms(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0,
-                                     one_shot ? kOneShotSlotBytes : 1, &plan);
+        rc = plan_call(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, one_shot ? kOneShotSlotBytes : 1, ov, &plan);
         if (rc) return rc;
         if ((plan.one_shot != 0) != one_shot) return fail(GPUK_ERR_UNSUPPORTED, "requested exchange mode is not available for this shape");
     }
-    if (!one_shot && ws->opt_rows_per_chunk > 0) plan.rows_per_chunk = std::min(ws->opt_rows_per_chunk, 64);
+    const bool use_ws = plan.ws != 0 && !one_shot && !sym;
+    if (!one_shot && !use_ws && ws->opt_rows_per_chunk > 0) plan.rows_per_chunk = std::min(ws->opt_rows_per_chunk, 64);
     if (ws->opt_ctas_per_sm > 0) plan.grid = std::min<int64_t>(plan.grid, static_cast<int64_t>(ws->sm_count) * ws->opt_ctas_per_sm);
     const int es = elem_size(a.dtype);
     memset(p, 0, sizeof(*p));
@@ -759,6 +796,17 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     p->row_vecs = plan.row_vecs;
     p->rows_per_chunk = plan.rows_per_chunk;
     p->seg_vecs = (plan.row_vecs + plan.cluster - 1) / plan.cluster;
+    p->cluster = plan.cluster;
+    if (use_ws) {
+        plan.grid = plan.ws_grid;
+        plan.rows_per_chunk = 1;
+        p->rows_per_chunk = 1;
+        p->tf = plan.ws_tf;
+        p->tr = plan.ws_tr;
+        p->ts = plan.ws_ts;
+        // no bounds checks in the finishing warps when every row, the last included, fills the tile
+        p->full = (plan.row_vecs == plan.ws_vpt * plan.ws_tf && p->total_vecs % plan.row_vecs == 0) ? 1 : 0;
+    }
     p->lead_push = std::max(1, ws->opt_lead_push > 0 ? ws->opt_lead_push : plan.lead_push);
     p->lead_reduce = std::max(1, ws->opt_lead_reduce > 0 ? ws->opt_lead_reduce : plan.lead_reduce);
     if (fused) fill_epilogue(a, q, plan.row_vecs, &p->ep);
@@ -782,16 +830,18 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         return fail(GPUK_ERR_TOO_LARGE, "message does not fit the reduce-scatter slots of the workspace");
 
     shape->world = ws->world;
-    shape->vpt = plan.vpt;
+    shape->vpt = use_ws ? plan.ws_vpt : plan.vpt;
     shape->two_shot = !one_shot;
     shape->fused = fused;
-    shape->threads = plan.threads;
+    shape->ws = use_ws ? 1 : 0;
+    shape->threads = use_ws ? plan.ws_tf + plan.ws_tr + plan.ws_ts : plan.threads;
     shape->cluster = plan.cluster;
     shape->grid = plan.grid;
     shape->sym = sym;
     // the grid must be co-resident: CTAs of equal index on different ranks wait for each other
-    const uint32_t key = static_cast<uint32_t>(a.dtype) | (plan.vpt << 4) | (one_shot ? 1u << 8 : 0u) |
-                         (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (static_cast<uint32_t>(plan.threads) << 12) |
+    const uint32_t key = static_cast<uint32_t>(a.dtype) | (shape->vpt << 4) | (one_shot ? 1u << 8 : 0u) |
+                         (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (use_ws ? 1u << 11 : 0u) |
+                         (static_cast<uint32_t>(shape->threads) << 12) |
                          (static_cast<uint32_t>(plan.cluster) << 24) | (static_cast<uint32_t>(sym) << 28);
     int64_t resident = 0;
     auto cached = ws->occupancy.find(key);
@@ -815,6 +865,7 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     int64_t clusters = std::min<int64_t>(std::min<int64_t>(plan.grid, resident) / plan.cluster, nchunks);
     if (clusters < 1) return fail(GPUK_ERR_UNSUPPORTED, "the GPU cannot hold one cluster of %d CTAs of the selected kernel", plan.cluster);
     shape->grid = static_cast<int>(clusters * plan.cluster);
+    if (ws->test_withhold_cluster) shape->cluster = 1;   // the kernels must notice and report it
     return GPUK_OK;
 }
 
@@ -852,16 +903,21 @@ int gpuk_residual_rms_quant(const void *in, const void *residual_in, const void 
     p.in = in;
     p.rows = plan.rows;
     fill_epilogue(a, q, plan.row_vecs, &p.ep);
-    // many rows: the staged kernel (rows through shared memory by bulk copies); GPUK_K1_STAGES = 0
-    // switches it off, 2 or 3 picks the ring depth (tuning knob, read once)
-    static const int env_stages = [] { const char *e = getenv("GPUK_K1_STAGES"); return e ? atoi(e) : -1; }();
-    const int stages = env_stages < 0 ? kDefaultK1Stages : env_stages;
-    static const int env_staged_min = [] { const char *e = getenv("GPUK_K1_STAGED_MIN_ROWS_PER_SM"); return e ? atoi(e) : -1; }();
-    const bool staged = stages >= 2 && plan.rows >= static_cast<int64_t>(env_staged_min >= 0 ? env_staged_min : kK1StagedMinRowsPerSm) * sms;
+    // rows beyond one per resident CTA: persistent CTAs that stage rows through shared memory by bulk
+    // copies, so that the next rows are in flight while the current one is reduced
+    const int stages = g_tuning.k1_stages < 0 ? kDefaultK1Stages : g_tuning.k1_stages;
+    const int64_t staged_min = g_tuning.k1_staged_min_rows < 0 ? kK1StagedMinRows(sms) : g_tuning.k1_staged_min_rows;
+    const bool staged = stages >= 1 && plan.rows >= staged_min;
     return by_dtype(dtype, [&](auto *t) {
         using T = std::remove_pointer_t<decltype(t)>;
         cudaError_t e = cudaErrorInvalidConfiguration;
-        if (staged) e = launch_norm_quant_staged<T>(p, plan.vpt, plan.threads, stages, sms, static_cast<cudaStream_t>(stream));
+        if (staged) {
+            // the persistent variant may use a wider CTA than the one-row-per-CTA kernel: fewer, faster row passes
+            int vpt = plan.vpt, threads = plan.threads;
+            const int want = g_tuning.k1_threads > 0 ? g_tuning.k1_threads : kDefaultK1Threads;
+            while (vpt > 1 && threads * 2 <= want) { vpt /= 2; threads = ((plan.row_vecs + vpt - 1) / vpt + 31) / 32 * 32; }
+            e = launch_norm_quant_staged<T>(p, vpt, threads, stages, sms, g_tuning.k1_ctas_per_sm, static_cast<cudaStream_t>(stream));
+        }
         if (e == cudaErrorInvalidConfiguration) {
             if (staged) cudaGetLastError();
             e = launch_norm_quant<T>(p, plan.vpt, plan.threads, plan.grid, static_cast<cudaStream_t>(stream));
@@ -869,6 +925,26 @@ int gpuk_residual_rms_quant(const void *in, const void *residual_in, const void 
         if (e != cudaSuccess) return fail(GPUK_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
         return static_cast<int>(GPUK_OK);
     });
+}
+
+int gpuk_set_tuning(const char *name, int64_t value) {
+    if (!name) return fail(GPUK_ERR_INVALID_ARGUMENT, "null option name");
+    const std::string n(name);
+    if (n == "k1_stages") {
+        if (value < -1 || value > 8) return fail(GPUK_ERR_INVALID_ARGUMENT, "k1_stages must be in [-1, 8]");
+        g_tuning.k1_stages = static_cast<int>(value);
+    } else if (n == "k1_threads") {
+        if (value != 0 && value != 256 && value != 512 && value != 1024) return fail(GPUK_ERR_INVALID_ARGUMENT, "k1_threads must be 0, 256, 512 or 1024");
+        g_tuning.k1_threads = static_cast<int>(value);
+    } else if (n == "k1_staged_min_rows") {
+        g_tuning.k1_staged_min_rows = value;
+    } else if (n == "k1_ctas_per_sm") {
+        if (value < 0 || value > 8) return fail(GPUK_ERR_INVALID_ARGUMENT, "k1_ctas_per_sm must be in [0, 8]");
+        g_tuning.k1_ctas_per_sm = static_cast<int>(value);
+    } else {
+        return fail(GPUK_ERR_INVALID_ARGUMENT, "unknown tuning option '%s'", name);
+    }
+    return GPUK_OK;
 }
 
 static int run_ar(gpuk_ws *ws, const CallArgs &a, void *stream) {
@@ -922,7 +998,8 @@ int gpuk_emulated_allreduce_rms(gpuk_ws *const *wss, int world_size, void *const
         int rc = build_ar_call(ws, a, force_mode, true, &host_params[r], &s);
         if (rc) return rc;
         if (r == 0) shape = s;
-        else if (s.grid != shape.grid || s.threads != shape.threads || s.vpt != shape.vpt || s.two_shot != shape.two_shot || s.sym != shape.sym)
+        else if (s.grid != shape.grid || s.threads != shape.threads || s.vpt != shape.vpt || s.two_shot != shape.two_shot ||
+                 s.sym != shape.sym || s.ws != shape.ws)
             return fail(GPUK_ERR_INVALID_ARGUMENT, "ranks disagree on the launch shape");
     }
     gpuk_ws *w0 = wss[0];

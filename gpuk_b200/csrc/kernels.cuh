@@ -71,14 +71,14 @@ constexpr int ar_resident_blocks() { return TWO_SHOT ? (VPT == 8 ? 1 : 2) : ar_m
 struct NormQuantParams {
     const void *in;     // [rows, hidden] T
     int64_t rows;
+    int stages;         // staged kernel: depth of the shared-memory ring (2 .. kMaxStages)
+    int full;           // 1: a row is exactly VPT * blockDim vectors (the launcher sets it): no bounds checks
     EpilogueArgs ep;
 };
+constexpr int kMaxStages = 8;
 
-template <typename T, int VPT>
-__global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>())
-    fused_norm_quant_kernel(const __grid_constant__ NormQuantParams p) {
-    __shared__ EpilogueSmem sm;
-    grid_dependency_sync();
+template <typename T, int VPT, bool FULL>
+__device__ __forceinline__ void norm_quant_rows(const NormQuantParams &p, EpilogueSmem &sm) {
     const float static_scale = p.ep.q.mode == kQuantStatic ? *p.ep.scale_out : 1.f;
     int parity = 0;
     for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
@@ -87,35 +87,46 @@ __global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>(
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * blockDim.x;
-            x[i] = v < p.ep.row_vecs ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
+            x[i] = (FULL || v < p.ep.row_vecs) ? ld_stream(src + v) : make_uint4(0, 0, 0, 0);
         }
         const RowSeg seg = whole_row(p.ep.row_vecs);
-        load_residual<T, VPT>(p.ep, seg, row, res);
-        row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
+        load_residual<T, VPT, FULL>(p.ep, seg, row, whole_cta(), res);
+        row_epilogue<T, VPT, FULL>(p.ep, seg, row, whole_cta(), x, res, sm, parity, static_scale);
     }
 }
 
-// The same operation for many rows: persistent CTAs take rows blockIdx.x, + gridDim.x, ... and
-// fetch each row (input and residual, contiguous in global memory) into a ring of STAGES
+template <typename T, int VPT>
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), tile_min_blocks<VPT>())
+    fused_norm_quant_kernel(const __grid_constant__ NormQuantParams p) {
+    __shared__ EpilogueSmem sm;
+    grid_dependency_sync();
+    if (p.full) norm_quant_rows<T, VPT, true>(p, sm);
+    else norm_quant_rows<T, VPT, false>(p, sm);
+}
+
+// The same operation on persistent CTAs: each takes rows blockIdx.x, + gridDim.x, ... and fetches
+// every row (input and residual, contiguous in global memory) into a ring of `stages`
 // shared-memory stages with two bulk copies that one thread issues.  A stage is refilled with
-// the row STAGES ahead as soon as every thread has taken its vectors out of it, so the loads of
-// the next rows are in flight during both block reductions of the current one.
-// Dynamic shared memory: STAGES * 2 * row_vecs * 16 bytes.  Needs at least two warps per CTA
+// the row `stages` ahead as soon as every thread has taken its vectors out of it, so the loads of
+// the next rows are in flight during both block reductions of the current one and the GPU's
+// memory system sees reads, arithmetic and writes of different rows at the same time.
+// Dynamic shared memory: stages * 2 * row_vecs * 16 bytes.  Needs at least two warps per CTA
 // (the refill relies on the block barrier inside the first reduction).
 template <int VPT>
-constexpr int staged_min_blocks() { return VPT == 4 ? 3 : (VPT == 8 ? 1 : (VPT == 2 ? 1 : 1)); }
+constexpr int staged_min_blocks() { return VPT == 4 ? 3 : 1; }
 
-template <typename T, int VPT, int STAGES>
-__global__ void __launch_bounds__(tile_max_threads<VPT>(), staged_min_blocks<VPT>())
-    fused_norm_quant_staged_kernel(const __grid_constant__ NormQuantParams p) {
-    extern __shared__ __align__(128) unsigned char stage_mem[];
-    __shared__ EpilogueSmem sm;
-    __shared__ __align__(8) uint64_t full[STAGES];
-    grid_dependency_sync();
+struct StagedSmem {
+    EpilogueSmem ep;
+    alignas(8) uint64_t full[kMaxStages];
+};
+
+template <typename T, int VPT, bool FULL>
+__device__ __forceinline__ void norm_quant_staged_rows(const NormQuantParams &p, unsigned char *stage_mem, StagedSmem &sm) {
+    uint64_t *full = sm.full;
+    const int stages = p.stages;
     const uint32_t row_bytes = static_cast<uint32_t>(p.ep.row_vecs) * 16u;
     const int64_t nk = blockIdx.x < p.rows ? (p.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    auto issue = [&](int64_t k) {
-        const int s = static_cast<int>(k % STAGES);
+    auto issue = [&](int64_t k, int s) {
         const int64_t row = blockIdx.x + k * gridDim.x;
         unsigned char *dst = stage_mem + static_cast<size_t>(s) * 2 * row_bytes;
         mbar_expect_bytes(&full[s], 2 * row_bytes);
@@ -123,29 +134,40 @@ __global__ void __launch_bounds__(tile_max_threads<VPT>(), staged_min_blocks<VPT
         bulk_load(dst + row_bytes, static_cast<const unsigned char *>(p.ep.residual) + row * row_bytes, row_bytes, &full[s]);
     };
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
         mbar_init_fence();
-        for (int64_t k = 0; k < STAGES && k < nk; ++k) issue(k);
+        for (int64_t k = 0; k < stages && k < nk; ++k) issue(k, static_cast<int>(k));
     }
     __syncthreads();
     const float static_scale = p.ep.q.mode == kQuantStatic ? *p.ep.scale_out : 1.f;
     const RowSeg seg = whole_row(p.ep.row_vecs);
+    int s = 0;
+    uint32_t phase = 0;
     for (int64_t k = 0; k < nk; ++k) {
-        const int s = static_cast<int>(k % STAGES);
-        mbar_wait(&full[s], static_cast<uint32_t>(k / STAGES) & 1u);
+        mbar_wait(&full[s], phase);
         const uint4 *sx = reinterpret_cast<const uint4 *>(stage_mem + static_cast<size_t>(s) * 2 * row_bytes);
         const uint4 *sr = sx + p.ep.row_vecs;
         uint4 x[VPT], res[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * blockDim.x;
-            x[i] = v < p.ep.row_vecs ? sx[v] : make_uint4(0, 0, 0, 0);
-            res[i] = v < p.ep.row_vecs ? sr[v] : make_uint4(0, 0, 0, 0);
+            x[i] = (FULL || v < p.ep.row_vecs) ? sx[v] : make_uint4(0, 0, 0, 0);
+            res[i] = (FULL || v < p.ep.row_vecs) ? sr[v] : make_uint4(0, 0, 0, 0);
         }
-        row_epilogue<T, VPT>(p.ep, seg, blockIdx.x + k * gridDim.x, x, res, sm, static_cast<int>(k & 1), static_scale,
-                             [&] { if (threadIdx.x == 0 && k + STAGES < nk) issue(k + STAGES); });
+        row_epilogue<T, VPT, FULL>(p.ep, seg, blockIdx.x + k * gridDim.x, whole_cta(), x, res, sm.ep, static_cast<int>(k & 1), static_scale,
+                                   [&] { if (threadIdx.x == 0 && k + stages < nk) issue(k + stages, s); });
+        if (++s == stages) { s = 0; phase ^= 1u; }
     }
+}
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(tile_max_threads<VPT>(), staged_min_blocks<VPT>())
+    fused_norm_quant_staged_kernel(const __grid_constant__ NormQuantParams p) {
+    extern __shared__ __align__(128) unsigned char stage_mem[];
+    __shared__ StagedSmem sm;
+    grid_dependency_sync();
+    if (p.full) norm_quant_staged_rows<T, VPT, true>(p, stage_mem, sm);
+    else norm_quant_staged_rows<T, VPT, false>(p, stage_mem, sm);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -160,6 +182,9 @@ struct ArParams {
     int row_vecs;
     int rows_per_chunk;    // rows a CTA moves through one stage before it turns to the next stage
     int seg_vecs;          // vectors of a row held by one CTA of the cluster that owns the row (all of them without a cluster)
+    int cluster;           // CTAs per thread-block cluster the host planned (seg_vecs was sized for it); checked at entry
+    int tf, tr, ts;        // warp-specialised two-shot: threads that finish rows / reduce slices / scatter (multiples of 32)
+    int full;              // ... 1: a row is exactly VPT * tf vectors, no bounds checks in the finishing warps
     int lead_push;         // two-shot: chunks by which the scatter runs ahead of the reduction (>= 1)
     int lead_reduce;       // two-shot: chunks by which the reduction runs ahead of the epilogue (>= 1)
     EpilogueArgs ep;       // fused only
@@ -260,7 +285,7 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
     }
     const RowSeg seg = RowSeg{v0, end_c, cl_rank, cl_size};
     if constexpr (FUSED) {
-        if (row_c >= 0) load_residual<T, VPT>(p.ep, seg, row_c, res);
+        if (row_c >= 0) load_residual<T, VPT>(p.ep, seg, row_c, whole_cta(), res);
     }
 
     // ---- consume: scatter
@@ -305,7 +330,7 @@ __device__ __forceinline__ void two_shot_step(const ArParams &p, int64_t ts, int
             }
         }
         if constexpr (FUSED) {
-            row_epilogue<T, VPT>(p.ep, seg, row_c, x, res, sm, parity, static_scale);
+            row_epilogue<T, VPT>(p.ep, seg, row_c, whole_cta(), x, res, sm, parity, static_scale);
             parity ^= 1;
         } else {
 #pragma unroll
@@ -344,6 +369,13 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
     int parity = 0;
     const int R = p.rows_per_chunk;
     const int nchunks = (p.rows + R - 1) / R;
+    // The segments of a row were sized for the planned cluster.  In a launch whose cluster attribute
+    // did not take effect a CTA would handle segment 0 only and leave the rest of every row unwritten:
+    // report it instead, before any ticket is taken or byte is stored.
+    if (cluster_size() != p.cluster) {
+        if (threadIdx.x == 0) record_status(st, kStatusClusterMismatch, p.rank, vb, TWO_SHOT ? kStageScatter : kStageOneShot, p.rank, cluster_size());
+        return;
+    }
 
     if constexpr (TWO_SHOT) {
         begin_call(st, nb, sm);
@@ -415,7 +447,7 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
                     }
                 }
             }
-            if constexpr (FUSED) load_residual<T, VPT>(p.ep, seg, row, res);   // in flight while the peers' rows arrive
+            if constexpr (FUSED) load_residual<T, VPT>(p.ep, seg, row, whole_cta(), res);   // in flight while the peers' rows arrive
             char *mine = p.peer_data[p.rank] + bo;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
@@ -437,7 +469,7 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
                 }
             }
             if constexpr (FUSED) {
-                row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
+                row_epilogue<T, VPT>(p.ep, seg, row, whole_cta(), x, res, sm, parity, static_scale);
                 parity ^= 1;
             } else {
 #pragma unroll
@@ -449,6 +481,189 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
         }
         if (nk == 0) begin_call(st, nb, sm);   // a CTA without rows still takes its ticket
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// two-shot exchange with specialised warps (the bandwidth regime: more rows than SMs)
+// ---------------------------------------------------------------------------------------
+// One CTA per SM; CTA b of every rank owns rows b, b + gridDim, ...  Its warps split into three
+// roles that each walk that row list on their own and meet only through the data:
+//
+//   scatter (ts threads)  reads the row of this rank's input and pushes slice j into slot
+//                         `rank` of rank j, for every peer j.  Waits for nothing, so it runs
+//                         ahead as far as NVLink lets it: the staging holds the whole message.
+//   reduce  (tr threads)  for the slice this rank owns: polls the N - 1 slots, adds this rank's
+//                         own slice straight from the input, sums in rank order in fp32, rounds
+//                         once and pushes the result into every rank's gather area.
+//   finish  (tf threads)  polls the gathered row, adds the residual and runs the epilogue (or,
+//                         for the plain all-reduce, copies it out).
+//
+// Every transfer is a push of self-announcing vectors (common.cuh), so no role ever fences or
+// signals; a role that waits for data only parks its own warps while the SM's schedulers run the
+// others, which is what a single thread-set walking the three roles in lock step cannot do.  The
+// row reductions of the finishing warps use a named barrier of their own.
+template <typename T, int NR>
+__device__ __forceinline__ void ws_scatter(const ArParams &p, int64_t ts_off, int vb, int nb, int tid, int nthreads) {
+    constexpr int U = NR == 2 ? 4 : (NR == 4 ? 2 : 1);   // slice vectors per thread and peer that travel together
+    const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
+    for (int row = vb; row < p.rows; row += nb) {
+        const int len = row_len(p, row);
+        const uint4 *src = in + static_cast<int64_t>(row) * p.row_vecs;
+        const int64_t slot_row = static_cast<int64_t>(row) * p.vpr;
+        for (int v0 = tid; v0 < p.vpr; v0 += U * nthreads) {
+            uint4 a[NR - 1][U];
+#pragma unroll
+            for (int d = 1; d < NR; ++d) {
+                const int j = (p.rank + d) % NR;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int vl = v0 + u * nthreads;
+                    if (vl < p.vpr && j * p.vpr + vl < len) a[d - 1][u] = ld_stream(src + j * p.vpr + vl);
+                }
+            }
+#pragma unroll
+            for (int d = 1; d < NR; ++d) {
+                const int j = (p.rank + d) % NR;
+                uint4 *dst = reinterpret_cast<uint4 *>(p.peer_data[j] + ts_off + p.rank * p.rs_slot_bytes) + slot_row;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int vl = v0 + u * nthreads;
+                    if (vl < p.vpr && j * p.vpr + vl < len) st_peer(dst + vl, payload<T>(a[d - 1][u]));
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int NR>
+__device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int vb, int nb, int tid, int nthreads) {
+    constexpr int U = NR == 2 ? 4 : (NR == 4 ? 2 : 1);   // slice vectors per thread in flight together: U * NR loads
+    const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
+    char *mine = p.peer_data[p.rank] + ts_off;
+    for (int row = vb; row < p.rows; row += nb) {
+        const int len = row_len(p, row);
+        const int64_t base = static_cast<int64_t>(row) * p.row_vecs + p.rank * p.vpr;
+        const int64_t slot_row = static_cast<int64_t>(row) * p.vpr;
+        for (int v0 = tid; v0 < p.vpr; v0 += U * nthreads) {
+            uint4 part[U][NR];
+            bool have[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int vl = v0 + u * nthreads;
+                have[u] = vl < p.vpr && p.rank * p.vpr + vl < len;
+                if (have[u]) {
+#pragma unroll
+                    for (int s2 = 0; s2 < NR; ++s2)
+                        part[u][s2] = s2 == p.rank ? ld_stream(in + base + vl)
+                                                   : ld_poll(reinterpret_cast<const uint4 *>(mine + s2 * p.rs_slot_bytes) + slot_row + vl);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (have[u]) {
+                    const int vl = v0 + u * nthreads;
+#pragma unroll
+                    for (int s2 = 0; s2 < NR; ++s2) {
+                        if (s2 != p.rank) {
+                            uint4 *addr = reinterpret_cast<uint4 *>(mine + s2 * p.rs_slot_bytes) + slot_row + vl;
+                            part[u][s2] = wait_landed(addr, part[u][s2], p.st, p.rank, kStageScatter, s2);
+                            st_empty(addr);
+                        }
+                    }
+                    const uint4 red = payload<T>(sum_in_rank_order<T, NR>(part[u]));
+#pragma unroll
+                    for (int d = 0; d < NR; ++d) {
+                        const int j = (p.rank + d) % NR;   // start with myself, then fan out: spreads the links
+                        st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + ts_off + p.ag_off) + base + vl, red);
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int VPT, bool FUSED, bool FULL>
+__device__ __forceinline__ void ws_finish(const ArParams &p, int64_t ts_off, int vb, int nb, const Group &grp, EpilogueSmem &sm) {
+    float static_scale = 1.f;
+    if constexpr (FUSED) {
+        if (p.ep.q.mode == kQuantStatic) static_scale = *p.ep.scale_out;
+    }
+    uint4 *ag = reinterpret_cast<uint4 *>(p.peer_data[p.rank] + ts_off + p.ag_off);
+    int parity = 0;
+    for (int row = vb; row < p.rows; row += nb) {
+        const int len = row_len(p, row);
+        const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
+        const RowSeg seg = RowSeg{0, len, 0, 1};
+        uint4 x[VPT], res[VPT];
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = grp.tid + i * grp.n;
+            x[i] = (FULL || v < len) ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
+        }
+        if constexpr (FUSED) load_residual<T, VPT, FULL>(p.ep, seg, row, grp, res);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = grp.tid + i * grp.n;
+            if (FULL || v < len) {
+                x[i] = wait_landed(ag + base + v, x[i], p.st, p.rank, kStageGather, v / p.vpr);
+                st_empty(ag + base + v);
+            }
+        }
+        if constexpr (FUSED) {
+            row_epilogue<T, VPT, FULL>(p.ep, seg, row, grp, x, res, sm, parity, static_scale);
+            parity ^= 1;
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int v = grp.tid + i * grp.n;
+                if (FULL || v < len) st_stream(reinterpret_cast<uint4 *>(p.out) + base + v, x[i]);
+            }
+        }
+    }
+}
+
+template <typename T, int NR, int VPT, bool FUSED>
+__device__ __forceinline__ void ar_ws_body(const ArParams &p, int vb, int nb, EpilogueSmem &sm) {
+    if (cluster_size() != p.cluster) {   // this kernel is planned without clusters
+        if (threadIdx.x == 0) record_status(p.st, kStatusClusterMismatch, p.rank, vb, kStageScatter, p.rank, cluster_size());
+        return;
+    }
+    begin_call(p.st, nb, sm);
+    __syncthreads();
+    const int64_t ts_off = static_cast<int64_t>(sm.seq & 1ull) * p.ts_stride;
+    const int tid = threadIdx.x;
+    if (tid < p.tf) {
+        const Group grp{tid, p.tf, 1};
+        if (p.full) ws_finish<T, VPT, FUSED, true>(p, ts_off, vb, nb, grp, sm);
+        else ws_finish<T, VPT, FUSED, false>(p, ts_off, vb, nb, grp, sm);
+    } else if (tid < p.tf + p.tr) {
+        ws_reduce<T, NR>(p, ts_off, vb, nb, tid - p.tf, p.tr);
+    } else {
+        ws_scatter<T, NR>(p, ts_off, vb, nb, tid - p.tf - p.tr, p.ts);
+    }
+}
+
+constexpr int kWsMaxThreads = 768;   // 512 finishing + 128 reducing + 128 scattering threads: one CTA per SM
+
+template <typename T, int NR, int VPT, bool FUSED>
+__global__ void __launch_bounds__(kWsMaxThreads, 1)
+    ar_ws_kernel(const __grid_constant__ ArParams p) {
+    __shared__ EpilogueSmem sm;
+    grid_dependency_sync();
+    ar_ws_body<T, NR, VPT, FUSED>(p, blockIdx.x, gridDim.x, sm);
+}
+
+// N ranks in one launch on one GPU (see ar_emulated_kernel).
+template <typename T, int NR, int VPT, bool FUSED>
+__global__ void __launch_bounds__(kWsMaxThreads, 1)
+    ar_ws_emulated_kernel(const ArParams *params_by_rank, int nb) {
+    __shared__ EpilogueSmem sm;
+    __shared__ ArParams p;
+    const int rank = blockIdx.x / nb;
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(ArParams) / 4); i += blockDim.x)
+        reinterpret_cast<uint32_t *>(&p)[i] = reinterpret_cast<const uint32_t *>(params_by_rank + rank)[i];
+    __syncthreads();
+    ar_ws_body<T, NR, VPT, FUSED>(p, blockIdx.x % nb, nb, sm);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -547,8 +762,8 @@ __device__ __noinline__ void sym_finish_rows(const ArParams &p, int r0, int r1, 
             const int v = threadIdx.x + i * blockDim.x;
             x[i] = v < p.row_vecs ? ld_staging(out + base + v) : make_uint4(0, 0, 0, 0);
         }
-        load_residual<T, VPT>(p.ep, seg, row, res);
-        row_epilogue<T, VPT>(p.ep, seg, row, x, res, sm, parity, static_scale);
+        load_residual<T, VPT>(p.ep, seg, row, whole_cta(), res);
+        row_epilogue<T, VPT>(p.ep, seg, row, whole_cta(), x, res, sm, parity, static_scale);
         parity ^= 1;
     }
 }

@@ -15,6 +15,7 @@ struct ArShape {
     int threads;
     int grid;        // CTAs per rank (a multiple of `cluster`)
     int cluster;     // CTAs per thread-block cluster (1: launched without a cluster attribute)
+    int ws;          // 1: the warp-specialised two-shot kernel (vpt: vectors per finishing thread, threads: all roles)
     int sym;         // 0: push exchange; 1: exchange through symmetric memory with peer loads;
                      // 2: the same with NVSwitch multicast (two_shot is true for 1 and 2)
 };
@@ -32,11 +33,13 @@ cudaError_t resident_ctas(const void *fn, int threads, int cluster, int sm_count
 template <typename T>
 cudaError_t launch_norm_quant(const NormQuantParams &p, int vpt, int threads, int grid, cudaStream_t stream);
 
-// Staged variant (rows through shared memory by bulk copies).  `grid` <= 0 asks for one CTA per
-// resident slot of the GPU; returns cudaErrorInvalidConfiguration when the tile is not built or
-// a row does not fit the shared memory, so that the caller can use the plain kernel.
+// Staged variant (rows through shared memory by bulk copies) on persistent CTAs: as many as fit
+// the GPU at once (at most `ctas_per_sm` per SM if that is positive), but no more than it takes
+// to give every CTA the same number of rows.  Returns cudaErrorInvalidConfiguration when the tile
+// is not built or a row does not fit the shared memory, so that the caller can use the plain kernel.
 template <typename T>
-cudaError_t launch_norm_quant_staged(const NormQuantParams &p, int vpt, int threads, int stages, int sm_count, cudaStream_t stream);
+cudaError_t launch_norm_quant_staged(const NormQuantParams &p, int vpt, int threads, int stages, int sm_count, int ctas_per_sm,
+                                     cudaStream_t stream);
 
 template <typename T>
 cudaError_t launch_ar(const ArParams &p, const ArShape &s, cudaStream_t stream);
@@ -48,6 +51,9 @@ cudaError_t launch_ar_emulated(const ArParams *params_by_rank, const ArShape &s,
 // CTAs of the instantiation `s` selects that fit the GPU at once (emulated = the one-GPU variant).
 template <typename T>
 cudaError_t ar_resident_ctas(const ArShape &s, bool emulated, int sm_count, int64_t *ctas);
+
+// Quantisation policy of an operator quant_type (include/gpuk_b200.h); false for an unknown one.
+bool quant_from_type(int quant_type, Quant *q);
 
 // Records the text gpuk_last_error() returns on this thread and hands `code` back
 // (defined next to gpuk_last_error).

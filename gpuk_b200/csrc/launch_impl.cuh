@@ -24,9 +24,20 @@ static const void *ar_sym_fn(const ArShape &s, bool emulated) {
                       : reinterpret_cast<const void *>(&ar_sym_kernel<T, NR, VPT, false>);
 }
 
+template <typename T, int NR, int VPT, bool FUSED>
+static const void *ar_ws_fn(bool emulated) {
+    return emulated ? reinterpret_cast<const void *>(&ar_ws_emulated_kernel<T, NR, VPT, FUSED>)
+                    : reinterpret_cast<const void *>(&ar_ws_kernel<T, NR, VPT, FUSED>);
+}
+
 template <typename T, int NR, int VPT>
 static const void *ar_fn_modes(const ArShape &s, bool emulated) {
     if (s.sym) return ar_sym_fn<T, NR, VPT>(s, emulated);
+    if (s.ws) {
+        if (s.fused) return ar_ws_fn<T, NR, VPT, true>(emulated);
+        if constexpr (VPT == 2) return ar_ws_fn<T, NR, VPT, false>(emulated);   // the plain all-reduce views rows of 1024 vectors
+        return nullptr;
+    }
     if (s.fused) return s.two_shot ? ar_fn<T, NR, VPT, true, true>(emulated) : ar_fn<T, NR, VPT, false, true>(emulated);
     if constexpr (VPT == 4) {   // the plain all-reduce is only built for the 4-vector tile
         return s.two_shot ? ar_fn<T, NR, VPT, true, false>(emulated) : ar_fn<T, NR, VPT, false, false>(emulated);
@@ -65,48 +76,73 @@ cudaError_t launch_norm_quant(const NormQuantParams &p, int vpt, int threads, in
     case 8: fn = norm_quant_fn<T, 8>(); break;
     default: return cudaErrorInvalidValue;
     }
-    void *args[] = {const_cast<NormQuantParams *>(&p)};
+    NormQuantParams q = p;
+    q.full = p.ep.row_vecs == vpt * threads ? 1 : 0;
+    void *args[] = {&q};
     return launch_kernel(fn, grid, threads, 1, false, args, stream);
 }
 
-template <typename T, int VPT, int STAGES>
-static cudaError_t launch_staged_one(const NormQuantParams &p, int threads, int sm_count, cudaStream_t stream) {
-    const void *fn = reinterpret_cast<const void *>(&fused_norm_quant_staged_kernel<T, VPT, STAGES>);
-    const size_t smem = static_cast<size_t>(STAGES) * 2 * p.ep.row_vecs * 16;
-    if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+template <typename T, int VPT>
+static cudaError_t launch_staged_one(const NormQuantParams &p0, int threads, int stages, int sm_count, int ctas_per_sm, cudaStream_t stream) {
+    const void *fn = reinterpret_cast<const void *>(&fused_norm_quant_staged_kernel<T, VPT>);
+    if (threads > tile_max_threads<VPT>()) return cudaErrorInvalidConfiguration;
+    NormQuantParams p = p0;
+    const size_t stage_bytes = static_cast<size_t>(2) * p.ep.row_vecs * 16;
+    if (stages > kMaxStages) stages = kMaxStages;
+    while (stages > 1 && stages * stage_bytes > 200 * 1024) --stages;
+    const size_t smem = stages * stage_bytes;
+    if (stages < 1 || smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+    p.stages = stages;
+    p.full = p.ep.row_vecs == VPT * threads ? 1 : 0;
     // per device: opt in to the shared-memory size and look up how many CTAs fit an SM
     // (this entry point has no workspace to keep the cache in, so it is guarded for concurrent callers)
     static std::mutex cache_mutex;
     static int per_sm_by_device[64] = {};
     static size_t smem_by_device[64] = {};
+    static int threads_by_device[64] = {};
+    static size_t smem_max_by_device[64] = {};
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return e;
     if (device < 0 || device >= 64) return cudaErrorInvalidConfiguration;
-    std::lock_guard<std::mutex> lock(cache_mutex);
-    if (per_sm_by_device[device] == 0 || smem_by_device[device] != smem) {
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        int per_sm = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, threads, smem);
-        if (e != cudaSuccess) return e;
-        if (per_sm <= 0) return cudaErrorInvalidConfiguration;
-        per_sm_by_device[device] = per_sm;
-        smem_by_device[device] = smem;
+    int per_sm;
+    {
+        std::lock_guard<std::mutex> lock(cache_mutex);
+        if (per_sm_by_device[device] == 0 || smem_by_device[device] != smem || threads_by_device[device] != threads) {
+            if (smem > smem_max_by_device[device]) {
+                e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+                if (e != cudaSuccess) return e;
+                smem_max_by_device[device] = smem;
+            }
+            int n = 0;
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, smem);
+            if (e != cudaSuccess) return e;
+            if (n <= 0) return cudaErrorInvalidConfiguration;
+            per_sm_by_device[device] = n;
+            smem_by_device[device] = smem;
+            threads_by_device[device] = threads;
+        }
+        per_sm = per_sm_by_device[device];
     }
-    const int64_t slots = static_cast<int64_t>(per_sm_by_device[device]) * sm_count;
-    const int grid = static_cast<int>(p.rows < slots ? p.rows : slots);
-    void *args[] = {const_cast<NormQuantParams *>(&p)};
+    if (ctas_per_sm > 0 && ctas_per_sm < per_sm) per_sm = ctas_per_sm;
+    const int64_t slots = static_cast<int64_t>(per_sm) * sm_count;
+    // every CTA takes the same number of rows (the last ones one fewer): no ragged last wave
+    const int64_t rounds = (p.rows + slots - 1) / slots;
+    const int grid = static_cast<int>((p.rows + rounds - 1) / rounds);
+    void *args[] = {&p};
     return launch_kernel(fn, grid, threads, 1, false, args, stream, smem);
 }
 
 template <typename T>
-cudaError_t launch_norm_quant_staged(const NormQuantParams &p, int vpt, int threads, int stages, int sm_count, cudaStream_t stream) {
+cudaError_t launch_norm_quant_staged(const NormQuantParams &p, int vpt, int threads, int stages, int sm_count, int ctas_per_sm,
+                                     cudaStream_t stream) {
     if (threads < 64) return cudaErrorInvalidConfiguration;
-    if (vpt == 4) return stages == 3 ? launch_staged_one<T, 4, 3>(p, threads, sm_count, stream) : launch_staged_one<T, 4, 2>(p, threads, sm_count, stream);
-    if (vpt == 2) return stages == 3 ? launch_staged_one<T, 2, 3>(p, threads, sm_count, stream) : launch_staged_one<T, 2, 2>(p, threads, sm_count, stream);
-    if (vpt == 1) return stages == 3 ? launch_staged_one<T, 1, 3>(p, threads, sm_count, stream) : launch_staged_one<T, 1, 2>(p, threads, sm_count, stream);
-    return cudaErrorInvalidConfiguration;
+    switch (vpt) {
+    case 1: return launch_staged_one<T, 1>(p, threads, stages, sm_count, ctas_per_sm, stream);
+    case 2: return launch_staged_one<T, 2>(p, threads, stages, sm_count, ctas_per_sm, stream);
+    case 4: return launch_staged_one<T, 4>(p, threads, stages, sm_count, ctas_per_sm, stream);
+    default: return cudaErrorInvalidConfiguration;
+    }
 }
 
 template <typename T>
@@ -135,7 +171,7 @@ cudaError_t ar_resident_ctas(const ArShape &s, bool emulated, int sm_count, int6
 
 #define GPUK_INSTANTIATE_LAUNCHERS(T)                                                                          \
     template cudaError_t launch_norm_quant<T>(const NormQuantParams &, int, int, int, cudaStream_t);           \
-    template cudaError_t launch_norm_quant_staged<T>(const NormQuantParams &, int, int, int, int, cudaStream_t); \
+    template cudaError_t launch_norm_quant_staged<T>(const NormQuantParams &, int, int, int, int, int, cudaStream_t); \
     template cudaError_t launch_ar<T>(const ArParams &, const ArShape &, cudaStream_t);                        \
     template cudaError_t launch_ar_emulated<T>(const ArParams *, const ArShape &, cudaStream_t);               \
     template cudaError_t ar_resident_ctas<T>(const ArShape &, bool, int, int64_t *);

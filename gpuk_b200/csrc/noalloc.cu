@@ -16,15 +16,18 @@
 //
 // Rules for callers.
 //   * The first call on a device sets the array up (address lookup, fill with the rest
-//     pattern, time budgets).  That first call launches a fill kernel and synchronises, so make
-//     it before any stream capture.
+//     pattern, time budgets).  That first call launches a fill kernel and synchronises the
+//     stream, so make it before any stream capture (during a capture it is refused).
 //   * All calls on a device share the one array and it keeps what the last call left in it:
-//     the exchange protocol leaves the staging at rest and keeps its call counter there, the
-//     status words are cleared at the start of every call.  Two calls that overlap on the GPU
-//     (different streams, or different threads) race on it: issue them one after another.
-//   * Every call first waits for the previous self-check on the device and looks at its status
-//     words; if that one gave up waiting (its outputs are then wrong), the array is put back
-//     to its initial state before the new exchange starts.
+//     the exchange protocol leaves the staging at rest, one call counter for all emulated ranks
+//     lives there, and the status words are cleared at the start of every call.  Two calls that
+//     overlap on the GPU (different streams, or different threads) race on it: issue them one
+//     after another on one stream.
+//   * Later calls are plain stream-ordered launches.  Each begins with a small kernel that looks
+//     at the status words the previous call left; if that call gave up waiting (its outputs are
+//     then wrong), the staging is put back to rest on the device before the new exchange starts.
+//   * gpuk_selfcheck_status tells the caller whether its own call completed: it waits for the
+//     stream and returns the status words of the last call (also without allocating).
 //
 // It calls no cudaMalloc / cudaFree and no allocating library routine.
 #include <cuda_runtime.h>
@@ -42,7 +45,8 @@ using namespace gpuk;
 namespace {
 
 constexpr int64_t kStaticMaxMessageBytes = 32 << 10;              // per emulated rank
-constexpr int64_t kStateBytes = 4096;                             // kMaxRanks LocalState records, 256 B apart
+constexpr int64_t kStateBytes = 4096;                             // kMaxRanks LocalState records, 256 B apart, then the call counter
+constexpr int64_t kCallCountOff = kMaxRanks * 256;                // one 64-bit count of exchanges for ALL emulated ranks
 constexpr int64_t kSlotBytes = kStaticMaxMessageBytes;            // scatter slot and one-shot slot
 constexpr int64_t kTsStride = (kMaxRanks + 1) * kSlotBytes;       // N scatter slots + gather area
 constexpr int64_t kOsOff = 2 * kTsStride;
@@ -66,12 +70,16 @@ __global__ void __launch_bounds__(ar_max_threads<VPT, TWO_SHOT>(), 1)
     ar_body<T, NR, VPT, TWO_SHOT, true>(ep.r[rank], blockIdx.x % nb, nb, sm);
 }
 
-__global__ void scratch_init_kernel(unsigned char *base, unsigned long long timeout_ns) {
+__device__ __forceinline__ void fill_staging_at_rest(unsigned char *base) {
     const size_t n = static_cast<size_t>(kScratchBytes - kStateBytes) / 16;
     uint4 *stage = reinterpret_cast<uint4 *>(base + kStateBytes);
     const uint4 e = make_uint4(kEmptyWord, kEmptyWord, kEmptyWord, kEmptyWord);
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x)
         stage[i] = e;
+}
+
+__global__ void scratch_init_kernel(unsigned char *base, unsigned long long timeout_ns) {
+    fill_staging_at_rest(base);
     if (blockIdx.x == 0 && threadIdx.x < kMaxRanks) {
         LocalState *st = reinterpret_cast<LocalState *>(base + threadIdx.x * 256);
         st->seq = 0;
@@ -80,14 +88,31 @@ __global__ void scratch_init_kernel(unsigned char *base, unsigned long long time
         st->timeout_ns = timeout_ns;
         for (int i = 0; i < kStatusWords; ++i) st->status[i] = 0;
     }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *reinterpret_cast<unsigned long long *>(base + kCallCountOff) = 0ull;
 }
 
-__global__ void scratch_clear_status_kernel(unsigned char *base, int world) {
-    if (threadIdx.x < world) {
+// First kernel of every call: if the previous call on this device gave up (any status word set),
+// the staging may hold unconsumed vectors and goes back to rest.  Status words are only read here.
+__global__ void scratch_repair_kernel(unsigned char *base) {
+    bool bad = false;
+    for (int r = 0; r < kMaxRanks; ++r) bad |= reinterpret_cast<const LocalState *>(base + r * 256)->status[0] != 0;
+    if (bad) fill_staging_at_rest(base);
+}
+
+// Second kernel of every call: clears the status words and gives EVERY emulated rank the same call
+// number.  The low bit of that number selects the staging buffer, so ranks that sat out earlier
+// calls (a smaller world size) must not keep a stale one.
+__global__ void scratch_begin_call_kernel(unsigned char *base) {
+    unsigned long long *count = reinterpret_cast<unsigned long long *>(base + kCallCountOff);
+    const unsigned long long c = *count;
+    __syncthreads();
+    if (threadIdx.x < kMaxRanks) {
         LocalState *st = reinterpret_cast<LocalState *>(base + threadIdx.x * 256);
+        st->seq = c << 16;
         st->abort = 0;
         for (int i = 0; i < kStatusWords; ++i) st->status[i] = 0;
     }
+    if (threadIdx.x == 0) *count = c + 1;
 }
 
 template <typename T, int NR>
@@ -114,12 +139,72 @@ const void *kernel_for_world(int world, int vpt, bool two_shot) {
 // Per-device set-up state (host side).
 struct DeviceScratch {
     unsigned char *base = nullptr;   // device address of g_static_scratch on that device
-    bool dirty = false;              // needs (re-)initialisation before the next exchange
+    bool ready = false;              // set-up done (array at rest, time budgets written)
 };
 DeviceScratch g_dev[kMaxDevices];
 std::mutex g_mu;
 
+// Device address of the scratch array on `device` (which must be current); the first call per
+// device looks it up and puts the array into its initial state (synchronises `s`).
+int scratch_base(int device, cudaStream_t s, unsigned char **out) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceScratch &d = g_dev[device];
+    if (!d.base) {
+        // in host code the array's name is a stand-in, not an address: ask the runtime for it
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p)
+            return set_last_error(GPUK_ERR_CUDA, "selfcheck: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        d.base = static_cast<unsigned char *>(p);
+    }
+    if (!d.ready) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) cudaGetLastError();
+        if (cap != cudaStreamCaptureStatusNone)
+            return set_last_error(GPUK_ERR_INVALID_ARGUMENT, "selfcheck: the first call on a device sets the scratch array up and "
+                                                             "synchronises; make it before the stream capture begins");
+        scratch_init_kernel<<<296, 256, 0, s>>>(d.base, 2000000000ull);
+        cudaError_t e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "selfcheck: scratch set-up failed: %s", cudaGetErrorString(e));
+        d.ready = true;
+    }
+    *out = d.base;
+    return GPUK_OK;
+}
+
 }  // namespace
+
+extern "C" int gpuk_selfcheck_status(uint32_t out[8], void *stream) {
+    if (!out) return set_last_error(GPUK_ERR_INVALID_ARGUMENT, "selfcheck: null output");
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
+        return set_last_error(GPUK_ERR_CUDA, "selfcheck: no current CUDA device");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    memset(out, 0, sizeof(uint32_t) * kStatusWords);
+    unsigned char *base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        if (!g_dev[device].ready) return GPUK_OK;   // no self-check has run on this device
+        base = g_dev[device].base;
+    }
+    alignas(16) unsigned char states[kMaxRanks * 256];
+    cudaError_t e = cudaMemcpyAsync(states, base, sizeof(states), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "selfcheck: reading the status words failed: %s", cudaGetErrorString(e));
+    for (int r = 0; r < kMaxRanks; ++r) {
+        const LocalState *st = reinterpret_cast<const LocalState *>(states + r * 256);
+        if (st->status[0] != 0) {
+            memcpy(out, st->status, sizeof(uint32_t) * kStatusWords);
+            if (out[0] == kStatusClusterMismatch)
+                return set_last_error(GPUK_ERR_BAD_LAUNCH, "selfcheck: emulated rank %u CTA %u ran in a thread-block cluster of %u CTAs, "
+                                      "not the planned size; nothing was written", out[1], out[2], out[6]);
+            return set_last_error(GPUK_ERR_PEER_TIMEOUT, "selfcheck: emulated rank %u CTA %u thread %u gave up waiting for data from rank %u "
+                                  "in stage %u (word seen 0x%08x)", out[1], out[2], out[5], out[4], out[3], out[6]);
+        }
+    }
+    return GPUK_OK;
+}
 
 extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allreduce_in, const void *residual_in,
                                             const void *rms_gamma, void *const *residual_out, void *const *norm_out,
@@ -133,14 +218,7 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
     if (numel == 0) return GPUK_OK;
 
     Quant q;
-    switch (quant_type) {
-    case GPUK_QUANT_NONE: q = {kQuantNone, 0, 0.f}; break;
-    case GPUK_QUANT_FP8_E4M3FN_240: q = {kQuantDynamic, 0, 240.f}; break;
-    case GPUK_QUANT_FP8_E4M3FNUZ_120: q = {kQuantDynamic, 1, 120.f}; break;
-    case GPUK_QUANT_FP8_E4M3FN_448: q = {kQuantDynamic, 0, 448.f}; break;
-    case GPUK_QUANT_FP8_E4M3FN_448_STATIC: q = {kQuantStatic, 0, 448.f}; break;
-    default: return set_last_error(GPUK_ERR_INVALID_ARGUMENT, "unknown quant_type %d", quant_type);
-    }
+    if (!quant_from_type(quant_type, &q)) return set_last_error(GPUK_ERR_INVALID_ARGUMENT, "unknown quant_type %d", quant_type);
     if (q.mode != kQuantNone && !scale_out) return set_last_error(GPUK_ERR_INVALID_ARGUMENT, "selfcheck: scale_out is null");
 
     // shape -> tile, through the library's own planner (pure host arithmetic)
@@ -172,35 +250,8 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     unsigned char *base = nullptr;
-    {
-        // once per device, with that device current: the device address of the scratch array
-        std::lock_guard<std::mutex> lock(g_mu);
-        DeviceScratch &d = g_dev[device];
-        if (!d.base) {
-            void *p = nullptr;
-            cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
-            if (e != cudaSuccess || !p)
-                return set_last_error(GPUK_ERR_CUDA, "selfcheck: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-            d.base = static_cast<unsigned char *>(p);
-            d.dirty = true;
-        }
-        if (!d.dirty) {
-            // did the previous self-check on this device give up?  (waits for it to finish)
-            alignas(16) unsigned char states[kStateBytes];
-            cudaError_t e = cudaMemcpy(states, d.base, kStateBytes, cudaMemcpyDeviceToHost);
-            if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "selfcheck: reading the scratch state failed: %s", cudaGetErrorString(e));
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (reinterpret_cast<const LocalState *>(states + r * 256)->status[0] != 0) d.dirty = true;
-        }
-        if (d.dirty) {
-            scratch_init_kernel<<<296, 256, 0, s>>>(d.base, 2000000000ull);
-            cudaError_t e = cudaGetLastError();
-            if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-            if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "selfcheck: scratch set-up failed: %s", cudaGetErrorString(e));
-            d.dirty = false;
-        }
-        base = d.base;
-    }
+    rc = scratch_base(device, s, &base);
+    if (rc) return rc;
 
     // co-residency: all emulated ranks' CTAs wait for each other inside one launch
     int64_t resident = 0;
@@ -230,6 +281,7 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
         p.row_vecs = plan.row_vecs;
         p.rows_per_chunk = 1;
         p.seg_vecs = (plan.row_vecs + plan.cluster - 1) / plan.cluster;
+        p.cluster = plan.cluster;
         p.lead_push = plan.lead_push > 0 ? plan.lead_push : 1;
         p.lead_reduce = plan.lead_reduce > 0 ? plan.lead_reduce : 1;
         p.ep.residual = residual_in;
@@ -240,6 +292,8 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
         p.ep.hidden = hidden;
         p.ep.row_vecs = plan.row_vecs;
         p.ep.eps = eps;
+        p.ep.hidden_f = static_cast<float>(hidden);
+        p.ep.inv_hidden = static_cast<float>(1.0 / static_cast<double>(hidden));
         p.ep.q = q;
         p.rank = r;
         p.vpr = (plan.row_vecs + world_size - 1) / world_size;
@@ -252,7 +306,10 @@ extern "C" int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allredu
         p.os_slot_bytes = kSlotBytes;
     }
 
-    scratch_clear_status_kernel<<<1, 32, 0, s>>>(base, world_size);
+    scratch_repair_kernel<<<296, 256, 0, s>>>(base);
+    scratch_begin_call_kernel<<<1, 32, 0, s>>>(base);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "selfcheck: launch failed: %s", cudaGetErrorString(e));
     int nb_arg = static_cast<int>(nb);
     void *args[] = {&ep, &nb_arg};
     e = launch_kernel(fn, static_cast<int>(nb * world_size), plan.threads, plan.cluster, true, args, s);

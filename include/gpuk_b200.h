@@ -33,7 +33,8 @@ enum {
     GPUK_ERR_UNSUPPORTED = 3,      /* shape or dtype outside what the kernels cover */
     GPUK_ERR_NOT_READY = 4,        /* peers' memory has not been opened yet */
     GPUK_ERR_TOO_LARGE = 5,        /* message exceeds the workspace created by gpuk_ws_create */
-    GPUK_ERR_PEER_TIMEOUT = 6      /* a device-side wait for a peer ran out (gpuk_ws_status) */
+    GPUK_ERR_PEER_TIMEOUT = 6,     /* a device-side wait for a peer ran out (gpuk_ws_status) */
+    GPUK_ERR_BAD_LAUNCH = 7        /* a kernel found itself in another launch shape than planned (gpuk_ws_status) */
 };
 
 /* element types of the activations */
@@ -208,6 +209,13 @@ typedef struct gpuk_plan {
     int cluster;        /* CTAs (one thread-block cluster) that share a row; 1 unless few rows must fill the GPU */
     int lead_push;      /* two-shot pipeline: chunks the scatter runs ahead of the reduction */
     int lead_reduce;    /* two-shot pipeline: chunks the reduction runs ahead of the epilogue */
+    /* two-shot exchange without clusters: one CTA per SM whose warps are specialised (scatter / reduce /
+     * finish); then grid is at most the SM count and the CTA has ws_tf + ws_tr + ws_ts threads */
+    int ws;             /* 1: that kernel runs this call (vpt, threads, grid, rows_per_chunk above describe the other
+                         * two-shot kernel, which the option "two_shot_ws" = 0 selects) */
+    int ws_grid;        /* its CTAs per rank */
+    int ws_vpt;         /* vectors of a row per finishing thread */
+    int ws_tf, ws_tr, ws_ts; /* finishing / reducing / scattering threads per CTA */
 } gpuk_plan;
 
 /* force_mode values of gpuk_emulated_allreduce_rms */
@@ -230,19 +238,32 @@ int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes);
 /*
  * Tuning options of the exchanges; all ranks must set the same values.  Names:
  * "rows_per_chunk" (rows a CTA takes through one pipeline role at a time, 0: default),
- * "ctas_per_sm" (cap on resident CTAs per SM, 0: default), "lead_push" / "lead_reduce" (pipeline
+ * "ctas_per_sm" (cap on resident CTAs per SM, 0: default), "cluster" (CTAs of a thread-block
+ * cluster that share a row: 1, 2, 4, 8, 0: default), "lead_push" / "lead_reduce" (pipeline
  * depths in chunks, 0: default), "oneshot_max_bytes", "sym_min_bytes" (smallest message that
  * takes the exchange through symmetric memory, 0: never), "sym_multicast" (1: reduce inside the
- * switch where a multicast mapping exists, 0: plain peer loads).
+ * switch where a multicast mapping exists, 0: plain peer loads).  "test_withhold_cluster" = 1 is a
+ * test hook: kernels are launched without their planned cluster attribute, which they must report
+ * (status code 3) instead of writing partial rows.
  * The reference fixes these at compile time (communicator.h:57-58, impl.h:375-376).
  */
 int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value);
+/*
+ * Process-wide tuning of the one-GPU kernel behind gpuk_residual_rms_quant (which has no
+ * workspace to carry options): "k1_stages" (shared-memory stages of the persistent variant: 2, 3,
+ * 0 = never use it, -1 = default), "k1_staged_min_rows" (rows from which that variant runs,
+ * -1 = default: more rows than the plain kernel has resident CTAs), "k1_ctas_per_sm" (cap on its
+ * resident CTAs per SM, 0 = as many as fit).  Not thread-safe against concurrent calls.
+ */
+int gpuk_set_tuning(const char *name, int64_t value);
 /* Budget of every device-side wait for a peer, in nanoseconds (default 2 s). */
 int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns);
 
 /*
  * Copies the workspace's device status words to `out` (synchronises the device):
- * out[0] = 0 ok / 1 wait timed out / 2 poll cap reached, out[1] = rank, out[2] = CTA,
+ * out[0] = 0 ok / 1 wait timed out / 2 poll cap reached / 3 the kernel ran in a thread-block
+ * cluster of another size than planned (out[6] = the size seen; it then wrote nothing and the
+ * call returns GPUK_ERR_BAD_LAUNCH), out[1] = rank, out[2] = CTA,
  * out[3] = stage (0 one-shot, 1 scatter, 2 gather, 3 self-test, 4 / 5 the two flags of the
  * exchange through symmetric memory), out[4] = peer whose data was
  * awaited, out[5] = thread, out[6] = word seen.  Returns GPUK_ERR_PEER_TIMEOUT if out[0] != 0.
@@ -284,15 +305,26 @@ int gpuk_emulated_allreduce_rms(gpuk_ws *const *ws, int world_size, void *const 
  * built into the library (about 8.5 MiB, held by every GPU that loads the library until the
  * process exits), which limits a message to 32 KiB per emulated rank (numel * element size);
  * larger requests return GPUK_ERR_TOO_LARGE.  Rows longer than 4096 16-byte vectors are not
- * built.  The first call on a device sets the array up (and synchronises): make it before any
- * stream capture.  All calls on a device share the array, which keeps the protocol's call
- * counter between calls; calls that overlap on the GPU race, so issue them one after another.
+ * built.  The first call on a device sets the array up and synchronises the stream: make it before
+ * any stream capture (during a capture that first call is refused).  Later calls are stream-ordered
+ * launches without a host synchronisation.  All calls on a device share the array, which keeps the
+ * protocol's call counter between calls and is not cleared otherwise; calls that overlap on the GPU
+ * race, so issue them one after another on one stream.  If a call gave up waiting (see
+ * gpuk_selfcheck_status), the next call puts the array back to rest on the device before it starts.
  * Allocates nothing (no cudaMalloc, cudaFree or allocating library call).
  */
 int gpuk_selfcheck_allreduce_rms(int world_size, void *const *allreduce_in, const void *residual_in,
                                  const void *rms_gamma, void *const *residual_out, void *const *norm_out,
                                  float *const *scale_out, int64_t numel, int hidden, int dtype, float eps,
                                  int quant_type, int force_mode, void *stream);
+/*
+ * No counterpart in the reference.  Waits for `stream` and copies the status words the last
+ * gpuk_selfcheck_allreduce_rms call on the current device left (layout as gpuk_ws_status; the
+ * first emulated rank that reported is returned): GPUK_OK, GPUK_ERR_PEER_TIMEOUT when a wait of
+ * that call ran out (its outputs are then not valid), GPUK_ERR_BAD_LAUNCH when the kernel ran in
+ * another cluster shape than planned.  Allocates nothing.
+ */
+int gpuk_selfcheck_status(uint32_t out[8], void *stream);
 
 #ifdef __cplusplus
 }

@@ -57,6 +57,7 @@ def test_two_shot_many_chunks_per_cta(world, lead_push, lead_reduce):
     0 keeps the default depths, the huge value runs the three stages strictly one after another."""
     parts, res, w = util.random_case(world, 1500, 1024, torch.bfloat16, seed=5 + world)
     with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        g.set_option("two_shot_ws", 0)      # the pipeline depths belong to the kernel without specialised warps
         g.set_option("lead_push", lead_push)
         g.set_option("lead_reduce", lead_reduce)
         outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, 3, force_mode=TWO_SHOT)
@@ -65,13 +66,16 @@ def test_two_shot_many_chunks_per_cta(world, lead_push, lead_reduce):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("rows_per_chunk", [1, 3])
+@pytest.mark.parametrize("rows_per_chunk", [1, 3, 0])
 @pytest.mark.parametrize("tokens,hidden,quant", [(1, 4096, 3), (129, 1024, 1), (700, 2048, 3), (37, 7168, 4), (1500, 1024, 0)])
 def test_two_shot_rows_per_chunk_and_repeated_calls(world, rows_per_chunk, tokens, hidden, quant):
-    """Chunks of one and of three rows (the last chunk ragged), twice on the same workspace."""
+    """The two-shot kernel whose CTAs walk scatter / reduce / finish in lock step, with chunks of one
+    and of three rows (the last chunk ragged), and (rows_per_chunk 0) whatever kernel the policy
+    picks -- the warp-specialised one where no cluster shares a row; twice on the same workspace."""
     parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 7 + tokens)
     static = 0.05 if quant == 4 else None
     with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        g.set_option("two_shot_ws", 0 if rows_per_chunk else 1)
         g.set_option("rows_per_chunk", rows_per_chunk)
         for _ in range(2):      # twice: the call counter and the staging parity must advance consistently
             outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=TWO_SHOT)
@@ -84,6 +88,7 @@ def test_plain_allreduce_with_three_rows_per_chunk():
     parts = [torch.randn(300 * 1024 + 64, generator=g0).to(torch.bfloat16) for _ in range(4)]
     want = eo.allreduce_t1(parts)
     with util.EmulatedGroup(4) as g:
+        g.set_option("two_shot_ws", 0)
         g.set_option("rows_per_chunk", 3)
         outs = g.plain([p.cuda() for p in parts], force_mode=TWO_SHOT)
     for got in outs:
@@ -186,6 +191,84 @@ def test_symmetric_exchange_interleaved_with_the_push_exchange_and_refused_witho
         with pytest.raises(cabi.GpukError) as e:
             g.fused([p.cuda() for p in big], res2.cuda(), w2.cuda(), 1e-6, 3, force_mode=SYMMETRIC)
         assert e.value.status == cabi.ERR_TOO_LARGE
+
+
+@pytest.mark.parametrize("mode,tokens,hidden", [(ONE_SHOT, 16, 4096), (TWO_SHOT, 16, 4096), (ONE_SHOT, 8, 8192)])
+def test_launch_without_the_planned_cluster_is_reported_and_writes_nothing(mode, tokens, hidden):
+    """A row is split over a thread-block cluster; if the launch runs without its cluster
+    attribute, every CTA would see itself as CTA 0 of a cluster of one and finish only the first
+    segment of each row.  The kernels compare the cluster they run in with the planned one and
+    report status 3 before they store anything: outputs keep their fill, the workspace says so,
+    and after gpuk_ws_clear_status the same workspaces exchange correctly."""
+    from gpuk_b200 import cabi
+    world = 2
+    plan = cabi.plan(world, tokens * hidden, hidden, oneshot_max_bytes=(2 << 20) if mode == ONE_SHOT else 1)
+    assert plan.cluster > 1
+    parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=tokens + hidden)
+    d_parts, d_res, d_w = [p.cuda() for p in parts], res.cuda(), w.cuda()
+    with util.EmulatedGroup(world) as g:
+        outs = [util.alloc_outputs(p, 3) for p in d_parts]
+        for o in outs:
+            o[0].fill_(7.0)
+            o[1].view(torch.uint8).fill_(0x55)
+        g.set_option("test_withhold_cluster", 1)
+        g.fused(d_parts, d_res, d_w, 1e-6, 3, force_mode=mode, outs=outs, check_status=False)
+        for r in range(world):
+            rc, st = g.status(r)
+            assert rc == cabi.ERR_BAD_LAUNCH, (rc, st)
+            assert st[0] == 3 and st[1] == r and st[6] == 1, st          # code, rank, cluster size seen
+            assert "cluster" in cabi.last_error()
+            assert torch.all(outs[r][0] == 7.0) and torch.all(outs[r][1].view(torch.uint8) == 0x55)
+            assert torch.all(outs[r][2] == -1.0)
+        g.set_option("test_withhold_cluster", 0)
+        g.clear_status()
+        got = g.fused(d_parts, d_res, d_w, 1e-6, 3, force_mode=mode)
+    _check_all_ranks(got, eo.epilogue_t1(parts, res, w, 1e-6, 3), 3)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("tokens,hidden,quant,dtype", [
+    (300, 8192, 3, torch.bfloat16), (301, 7168, 3, torch.bfloat16), (160, 16384, 1, torch.bfloat16), (150, 32768, 3, torch.bfloat16),
+    (999, 136, 4, torch.bfloat16), (333, 2056, 0, torch.bfloat16), (200, 4096, 2, torch.float16), (180, 1000, 3, torch.float32)])
+def test_two_shot_with_specialised_warps(world, tokens, hidden, quant, dtype):
+    """The kernel of the bandwidth regime: one CTA per SM whose warps scatter, reduce and finish rows
+    independently.  Tiles of 1, 2, 4 and 8 vectors per finishing thread, rows that fill their tile and
+    rows that do not, slices that do not divide the row (2056 / 8 = 257 vectors over 2, 4, 8 ranks), all
+    element types and policies; three calls in a row so both staging buffers are reused."""
+    from gpuk_b200 import cabi
+    plan = cabi.plan(world, tokens * hidden, hidden, dtype=cabi.dtype_code(dtype), oneshot_max_bytes=1)
+    assert plan.ws == 1 and plan.ws_tf + plan.ws_tr + plan.ws_ts <= 768 and plan.ws_vpt * plan.ws_tf >= plan.row_vecs
+    static = 0.05 if quant == 4 else None
+    with util.EmulatedGroup(world, max_bytes=16 << 20) as g:
+        for call in range(3):
+            parts, res, w = util.random_case(world, tokens, hidden, dtype, seed=world * 11 + tokens + call)
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=TWO_SHOT)
+            want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
+            for got in outs:
+                util.check_against_oracle(got, want, quant, exact_residual=dtype != torch.float32)
+                assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8))
+
+
+def test_prefill_distribution_with_outliers_eight_ranks():
+    """Config 4's inputs (0.1 % of the partials multiplied by 20, seeds of the benchmark) at
+    2048 of its 16384 rows, eight ranks, two-shot: more chunks than resident CTAs."""
+    cfg = oin.CONFIGS["c4"]
+    parts, res, w = oin.make_case(cfg, 8, tokens=2048)
+    with util.EmulatedGroup(8, max_bytes=32 << 20) as g:
+        outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), cfg.eps, cfg.quant_type, force_mode=TWO_SHOT)
+    want = eo.epilogue_t1(parts, res, w, cfg.eps, cfg.quant_type)
+    _check_all_ranks(outs, want, cfg.quant_type)
+
+
+def test_mid_batch_config_two_and_eight_ranks():
+    """Config 3 (1024 x 8192, the benchmark's seeds) as the policy runs it."""
+    cfg = oin.CONFIGS["c3"]
+    for world in (2, 8):
+        parts, res, w = oin.make_case(cfg, world)
+        with util.EmulatedGroup(world, max_bytes=16 << 20) as g:
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), cfg.eps, cfg.quant_type)
+        want = eo.epilogue_t1(parts, res, w, cfg.eps, cfg.quant_type)
+        _check_all_ranks(outs, want, cfg.quant_type)
 
 
 def test_benchmark_decode_config_eight_ranks():

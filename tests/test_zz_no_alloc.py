@@ -21,10 +21,14 @@ from oracle import epilogue_oracle as eo  # noqa: E402
 from tests import util                    # noqa: E402
 
 
-def _selfcheck(parts, residual, weight, eps, quant, static_scale, mode):
+def _selfcheck(parts, residual, weight, eps, quant, static_scale, mode, check_free=True):
     world = len(parts)
     outs = [util.alloc_outputs(p, quant, static_scale) for p in parts]
     arr = lambda ts: (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])
+    torch.cuda.synchronize()
+    # free bytes as the driver counts them: a cudaMalloc inside the library cannot hide from this
+    # (torch.cuda.memory_allocated() only sees PyTorch's own caching allocator)
+    free_before = torch.cuda.mem_get_info()[0]
     before = torch.cuda.memory_allocated()
     cabi.check(cabi.lib.gpuk_selfcheck_allreduce_rms(
         world, arr(parts), util.ptr(residual), util.ptr(weight), arr([o[0] for o in outs]), arr([o[1] for o in outs]),
@@ -32,6 +36,10 @@ def _selfcheck(parts, residual, weight, eps, quant, static_scale, mode):
         mode, util.stream_ptr()))
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    if check_free:
+        assert torch.cuda.mem_get_info()[0] == free_before
+    st = (ctypes.c_uint32 * 8)()
+    assert cabi.lib.gpuk_selfcheck_status(st, util.stream_ptr()) == cabi.OK, (list(st), cabi.last_error())
     return [(o[0].cpu(), o[1].cpu(), o[2].cpu() if quant else None) for o in outs]
 
 
@@ -45,7 +53,9 @@ def test_matches_workspace_based_entry_point_twice_in_a_row(world, tokens, hidde
             parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world * 13 + tokens + call)
             d_parts, d_res, d_w = [p.cuda() for p in parts], res.cuda(), w.cuda()
             want = g.fused(d_parts, d_res, d_w, 1e-6, quant, static, force_mode=mode)
-            got = _selfcheck(d_parts, d_res, d_w, 1e-6, quant, static, mode)
+            # the first launch of a kernel loads its code onto the device (lazy module loading), which
+            # the driver's free-byte count shows: the count is compared from the second call on
+            got = _selfcheck(d_parts, d_res, d_w, 1e-6, quant, static, mode, check_free=call > 0)
             oracle = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
             for r in range(world):
                 # same kernels, same summation order: identical bits, well inside the parity bars
@@ -54,6 +64,29 @@ def test_matches_workspace_based_entry_point_twice_in_a_row(world, tokens, hidde
                 if quant:
                     assert torch.equal(got[r][2], want[r][2]), (call, r)
                 util.check_against_oracle(got[r], oracle, quant)
+
+
+def test_world_size_changes_between_calls():
+    """All emulated ranks share ONE call counter (its low bit selects the staging buffer): after a
+    two-rank call, ranks 2..7 must not be one call behind ranks 0 and 1.  World 2, then 4, then 8,
+    and back, in both exchange modes, each against the workspace-based entry point."""
+    seq = [(2, 1), (4, 1), (8, 1), (2, 2), (8, 2), (4, 2), (8, 1), (2, 1), (4, 2)]
+    for i, (world, mode) in enumerate(seq):
+        parts, res, w = util.random_case(world, 3, 2048, torch.bfloat16, seed=500 + i)
+        d_parts, d_res, d_w = [p.cuda() for p in parts], res.cuda(), w.cuda()
+        with util.EmulatedGroup(world, max_bytes=1 << 20) as g:
+            want = g.fused(d_parts, d_res, d_w, 1e-6, 3, force_mode=mode)
+        got = _selfcheck(d_parts, d_res, d_w, 1e-6, 3, None, mode, check_free=False)
+        for r in range(world):
+            assert torch.equal(got[r][0].view(torch.uint8), want[r][0].view(torch.uint8)), (i, r)
+            assert torch.equal(got[r][1].view(torch.uint8), want[r][1].view(torch.uint8)), (i, r)
+            assert torch.equal(got[r][2], want[r][2]), (i, r)
+
+
+def test_status_reads_ok_when_no_call_gave_up():
+    st = (ctypes.c_uint32 * 8)()
+    assert cabi.lib.gpuk_selfcheck_status(st, util.stream_ptr()) == cabi.OK
+    assert list(st) == [0] * 8
 
 
 def test_refuses_messages_beyond_the_built_in_scratch():
