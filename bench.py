@@ -671,6 +671,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-model", action="store_true", help="skip the decoder-model step (config 5) in the sweep")
     ap.add_argument("--crossover", action="store_true", help="also time one-shot / two-shot / symmetric over token counts")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
+                    help="workspace tuning option for the exchange (gpuk_ws_set_option), e.g. two_shot_ws=0; repeatable")
     ap.add_argument("--case", choices=["norm_quant", "emulated"], help="run one short fixed case of a kernel and exit")
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=8192)
@@ -707,6 +709,9 @@ def main():
     oin = load_workloads()
 
     env = gpuk.GPUKDistEnv(group=None, device_id=local_rank)
+    for item in args.opt:
+        name, value = item.split("=", 1)
+        env.set_option(name, int(value))
 
     def barrier():
         if world > 1:
@@ -780,7 +785,7 @@ def main():
             "metric": METRIC, "value": us, "unit": "us/call", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": us * 1e-3, "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_dict(cfg, world),
+            "config": config_dict(cfg, world, **({"options": args.opt} if args.opt else {})),
             "l2": f"rotating {head['buffer_sets']} buffer sets (> 4x L2)",
             "timed": f"median of {head['blocks']} blocks of {args.steps} calls, max over ranks per block",
             "parity": head["parity"],

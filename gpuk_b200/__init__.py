@@ -109,18 +109,24 @@ class GPUKDistEnv:
       the module-level FP8 policy);
     * inputs are never registered or copied into staging by the host, so ``capture`` /
       ``consume_capture`` exchange nothing (they still synchronise the group as before);
-    * ``symmetric_bytes`` (keyword-only, or ``GPUK_SYMMETRIC_BYTES``) adds a second exchange for
-      large messages: a buffer of that size from ``torch.distributed._symmetric_memory`` is
-      attached to the workspace, and where the NVSwitch offers a multicast mapping the reduction
-      runs inside the switch.  ``set_option("sym_min_bytes", n)`` sends fused calls of at least
-      ``n`` bytes through it.
+    * ``gather_multicast`` (keyword-only; default: on from four ranks where it can be had,
+      ``GPUK_GATHER_MULTICAST=0`` switches it off): the gather areas of the two-shot exchange are placed in a buffer from
+      ``torch.distributed._symmetric_memory`` and, where the NVSwitch offers a multicast mapping,
+      a reduced slice is sent ONCE and copied to all ranks by the switch (``multimem.st``) instead of
+      once per peer.  Pure data movement: results are bit-identical either way.  Without a
+      multicast mapping (or if the allocation fails) the exchange pushes to every peer itself.
+    * ``symmetric_bytes`` (keyword-only, or ``GPUK_SYMMETRIC_BYTES``, with ``gather_multicast=False``)
+      adds a second exchange for large messages: a buffer of that size from
+      ``torch.distributed._symmetric_memory`` is attached to the workspace, and where the NVSwitch
+      offers a multicast mapping the reduction runs inside the switch (which rounds 16-bit sums its
+      own way).  ``set_option("sym_min_bytes", n)`` sends fused calls of at least ``n`` bytes through it.
     """
 
     _SUPPORTED_WORLD_SIZES = [2, 4, 8]
 
     def __init__(self, group=None, device_id: int = None, max_size_in_bytes=16384 * 16384,
                  comm_ptrs_buf_len=1024 * 256, dtype: torch.dtype = torch.bfloat16, *, symmetric_bytes: Optional[int] = None,
-                 _ops=None) -> None:
+                 gather_multicast: Optional[bool] = None, _ops=None) -> None:
         self._o = _ops or _TorchOps
         self.group = group
         self.device_id = device_id
@@ -152,7 +158,15 @@ class GPUKDistEnv:
         self.barrier()
         if symmetric_bytes is None and os.environ.get("GPUK_SYMMETRIC_BYTES"):
             symmetric_bytes = int(os.environ["GPUK_SYMMETRIC_BYTES"])
-        if symmetric_bytes:
+        if gather_multicast is None:
+            # measured on B200 (224 MiB message): eight ranks 663 us with the switch copying the gathered slices,
+            # 741 us without; two ranks 557 us with, 403 us without (nothing to save when there is one peer)
+            gather_multicast = (self.world_size >= 4 and not symmetric_bytes and _ops is None
+                                and os.environ.get("GPUK_GATHER_MULTICAST", "1") != "0")
+        self.gather_multicast = False
+        if gather_multicast and not symmetric_bytes:
+            self._try_gather_multicast(int(max_size_in_bytes))
+        elif symmetric_bytes:
             self._attach_symmetric(int(symmetric_bytes))
 
     def _attach_symmetric(self, nbytes: int) -> None:
@@ -170,6 +184,22 @@ class GPUKDistEnv:
         cabi.check(cabi.lib.gpuk_ws_attach_symmetric(ctypes.c_void_p(self.fptr), bases, self.world_size,
                                                      ctypes.c_void_p(mc) if mc else None, nbytes))
         self.multicast = bool(mc)
+        self.barrier()
+
+    def _try_gather_multicast(self, max_size_in_bytes: int) -> None:
+        """Gather areas in symmetric memory behind the NVSwitch multicast address, where that can be had.
+        Every rank must reach the same decision, so the outcome is agreed on through the group."""
+        ok = 0
+        try:
+            self._attach_symmetric(2 * ((max_size_in_bytes + 255) // 256 * 256) + cabi.SYM_FLAG_BYTES + 1024)
+            ok = 1 if self.multicast else 0
+        except Exception:   # no symmetric memory in this build / on this fabric: the exchange pushes to every peer
+            ok = 0
+        agreed = [None] * self.world_size
+        dist.all_gather_object(agreed, ok, group=self.group)
+        if all(agreed):
+            self.set_option("gather_multicast", 1)
+            self.gather_multicast = True
         self.barrier()
 
     def check(self) -> None:

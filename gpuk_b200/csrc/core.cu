@@ -148,6 +148,8 @@ struct Tuning {
 };
 Tuning g_tuning;
 constexpr int kWsFinishThreads = 512;           // warp-specialised two-shot kernel: threads per role (kernels.cuh: kWsMaxThreads)
+constexpr int kWsScatterLeadShort = 2;          // ... rows the scatter may run ahead of the finish: few rows per CTA / many
+constexpr int kWsScatterLeadLong = 8;
 constexpr int kWsReduceThreads = 128;
 constexpr int kWsScatterThreads = 128;
 constexpr int kDefaultLeadPush = 1;             // two-shot pipeline depths (chunks), see ar_body
@@ -240,6 +242,8 @@ struct gpuk_ws {
     int opt_rows_per_chunk = 0, opt_ctas_per_sm = 0;   // 0 = default
     int opt_lead_push = 0, opt_lead_reduce = 0;
     int opt_cluster = 0;                 // CTAs per row (0: the planner decides)
+    int opt_ws_scatter_lead = -1;        // rows its scatter may run ahead of its finish (-1: default, 0: unbounded)
+    int opt_ws_tf = 0, opt_ws_tr = 0, opt_ws_ts = 0;   // threads per role of that kernel (0: default)
     int opt_two_shot_ws = 1;             // 1: two-shot calls without clusters run the warp-specialised kernel
     bool test_withhold_cluster = false;  // test hook: launch without the planned cluster attribute
     // exchange through symmetric memory (gpuk_ws_attach_symmetric)
@@ -248,6 +252,7 @@ struct gpuk_ws {
     int64_t sym_cap = 0, sym_flag_off = 0;   // largest message; offset of the flags
     int64_t sym_min_bytes = 0;               // messages from this size take it (0: never automatically)
     bool sym_use_mc = true;                  // reduce inside the switch where a multicast mapping exists
+    bool gather_multicast = false;           // two-shot gather through the multicast address (symmetric memory holds the gather areas)
     std::map<uint32_t, int64_t> occupancy;   // CTAs resident on the whole GPU, by kernel instantiation
 };
 
@@ -278,6 +283,7 @@ struct PlanOverrides {
     int rows_per_chunk = 0;
     bool allow_cluster = true;   // false: every row stays in one CTA (the exchange through symmetric memory)
     bool allow_ws = true;        // false: never the warp-specialised two-shot kernel
+    int ws_tf = 0, ws_tr = 0, ws_ts = 0;   // its threads per role (0: default)
 };
 
 static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int sm_count, int ctas_per_sm_limit,
@@ -353,14 +359,16 @@ static int plan_call(int world_size, int64_t numel, int hidden, int dtype, int s
     out->ws_vpt = out->ws_tf = out->ws_tr = out->ws_ts = out->ws_grid = 0;
     if (world_size > 1 && !one_shot && cluster == 1 && ov.allow_ws) {
         int wv = fused ? 1 : 2;   // the plain all-reduce is built for the 2-vector tile only
-        while (wv < 8 && (row_vecs + wv - 1) / wv > kWsFinishThreads) wv *= 2;
+        const int tf_max = ov.ws_tf > 0 && fused ? ov.ws_tf : kWsFinishThreads;
+        while (wv < 8 && (row_vecs + wv - 1) / wv > tf_max) wv *= 2;
         const int tf = ((row_vecs + wv - 1) / wv + 31) / 32 * 32;
-        if (tf <= kWsFinishThreads) {
+        const int tr = ov.ws_tr > 0 ? ov.ws_tr : kWsReduceThreads, tsc = ov.ws_ts > 0 ? ov.ws_ts : kWsScatterThreads;
+        if (tf <= tf_max && tf + tr + tsc <= kWsMaxThreads) {
             out->ws = 1;
             out->ws_vpt = wv;
             out->ws_tf = tf;
-            out->ws_tr = kWsReduceThreads;
-            out->ws_ts = kWsScatterThreads;
+            out->ws_tr = tr;
+            out->ws_ts = tsc;
             out->ws_grid = static_cast<int>(std::min<int64_t>(rows, sm_count));
         }
     }
@@ -625,8 +633,25 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     } else if (n == "two_shot_ws") {
         if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "two_shot_ws must be 0 or 1");
         ws->opt_two_shot_ws = static_cast<int>(value);
+    } else if (n == "ws_finish_threads" || n == "ws_reduce_threads" || n == "ws_scatter_threads") {
+        if (value < 0 || value > 512 || value % 32) return fail(GPUK_ERR_INVALID_ARGUMENT, "%s must be a multiple of 32 in [0, 512]", name);
+        (n == "ws_finish_threads" ? ws->opt_ws_tf : (n == "ws_reduce_threads" ? ws->opt_ws_tr : ws->opt_ws_ts)) = static_cast<int>(value);
+    } else if (n == "ws_scatter_lead") {
+        if (value < -1 || value > (1 << 20)) return fail(GPUK_ERR_INVALID_ARGUMENT, "ws_scatter_lead must be in [-1, 2^20]");
+        ws->opt_ws_scatter_lead = static_cast<int>(value);
     } else if (n == "test_withhold_cluster") {
         ws->test_withhold_cluster = value != 0;
+    } else if (n == "gather_multicast") {
+        if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "gather_multicast must be 0 or 1");
+        if (value && (!ws->sym[ws->rank] || !ws->sym_mc))
+            return fail(GPUK_ERR_NOT_READY, "gather_multicast needs symmetric memory with a multicast mapping (gpuk_ws_attach_symmetric)");
+        if (value) {
+            // the two halves of the symmetric buffer become the gather areas of the two call parities: at rest
+            GPUK_CUDA(cudaSetDevice(ws->device));
+            GPUK_CUDA(cudaDeviceSynchronize());
+            GPUK_CUDA(fill_empty(ws->sym[ws->rank], 2 * ws->sym_cap));
+        }
+        ws->gather_multicast = value != 0;
     } else if (n == "sym_multicast") {
         if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "sym_multicast must be 0 or 1");
         ws->sym_use_mc = value != 0;
@@ -670,6 +695,7 @@ int gpuk_ws_clear_status(gpuk_ws *ws) {
     GPUK_CUDA(cudaMemset(&ws->st->abort, 0, sizeof(uint32_t)));
     // an exchange that gave up may have left vectors unconsumed: put the staging back to rest
     GPUK_CUDA(fill_empty(ws->data, ws->data_bytes));
+    if (ws->gather_multicast && ws->sym[ws->rank]) GPUK_CUDA(fill_empty(ws->sym[ws->rank], 2 * ws->sym_cap));
     return GPUK_OK;
 }
 
@@ -749,6 +775,9 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     PlanOverrides ov;
     ov.cluster = ws->opt_cluster;
     ov.allow_ws = ws->opt_two_shot_ws != 0;
+    ov.ws_tf = ws->opt_ws_tf;
+    ov.ws_tr = ws->opt_ws_tr;
+    ov.ws_ts = ws->opt_ws_ts;
     int rc = plan_call(ws->world, a.numel, a.hidden, a.dtype, ws->sm_count, 0, ws->oneshot_max_bytes, ov, &plan);
     if (rc) return rc;
     if (plan.message_bytes > ws->cap)
@@ -757,9 +786,11 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     bool one_shot = plan.one_shot != 0;
     int sym = 0;
     if (force_mode == GPUK_MODE_SYMMETRIC ||
-        (force_mode == GPUK_MODE_AUTO && fused && !one_shot && ws->sym[ws->rank] && ws->sym_min_bytes > 0 &&
+        (force_mode == GPUK_MODE_AUTO && fused && !one_shot && ws->sym[ws->rank] && ws->sym_min_bytes > 0 && !ws->gather_multicast &&
          plan.message_bytes >= ws->sym_min_bytes && plan.message_bytes <= ws->sym_cap)) {
         if (!fused) return fail(GPUK_ERR_UNSUPPORTED, "the exchange through symmetric memory is built for the fused operator only");
+        if (ws->gather_multicast)
+            return fail(GPUK_ERR_UNSUPPORTED, "the symmetric buffer holds the gather areas (option gather_multicast): the exchange through symmetric memory is off");
         if (!ws->sym[ws->rank]) return fail(GPUK_ERR_NOT_READY, "no symmetric memory attached to this workspace");
         if (plan.message_bytes > ws->sym_cap)
             return fail(GPUK_ERR_TOO_LARGE, "message of %lld bytes exceeds the symmetric buffer (%lld bytes per message)",
@@ -801,6 +832,16 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         plan.grid = plan.ws_grid;
         plan.rows_per_chunk = 1;
         p->rows_per_chunk = 1;
+        // rows the scatter may run ahead of the finish.  Measured at eight ranks with the multicast gather, 2 / 8 rows:
+        // 16 MiB (7 rows per CTA) 59.2 / 61.5 us, 224 MiB (111 rows per CTA) 681 / 663 us; two ranks, 224 MiB: 439 / 407 us.
+        const int64_t rows_per_cta = (plan.rows + plan.ws_grid - 1) / std::max(plan.ws_grid, 1);
+        p->scatter_lead = ws->opt_ws_scatter_lead < 0 ? (rows_per_cta >= 32 ? kWsScatterLeadLong : kWsScatterLeadShort) : ws->opt_ws_scatter_lead;
+        // gather areas: in the workspace, or in symmetric memory behind the NVSwitch multicast address
+        const bool mc = ws->gather_multicast && ws->sym_mc && !emulated && plan.message_bytes <= ws->sym_cap;
+        for (int r = 0; r < ws->world; ++r)
+            p->ag_base[r] = mc ? ws->sym[r] : static_cast<char *>(ws->peer_data[r]) + ws->ag_off;
+        p->ag_stride = mc ? ws->sym_cap : ws->ts_stride;
+        p->ag_mc = mc ? ws->sym_mc : nullptr;
         p->tf = plan.ws_tf;
         p->tr = plan.ws_tr;
         p->ts = plan.ws_ts;

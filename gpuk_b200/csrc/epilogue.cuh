@@ -56,6 +56,7 @@ struct alignas(16) EpilogueSmem {
     float red[2][2][32];
     float cl[2][2][8];
     unsigned long long seq;   // number of the running exchange, fetched once per CTA (begin_call)
+    int rows_finished;        // warp-specialised two-shot kernel: rows this CTA's finishing warps have completed
 };
 
 // The RMSNorm weight is re-read for every row (it stays in L1/L2) instead of being held in

@@ -184,6 +184,7 @@ struct ArParams {
     int seg_vecs;          // vectors of a row held by one CTA of the cluster that owns the row (all of them without a cluster)
     int cluster;           // CTAs per thread-block cluster the host planned (seg_vecs was sized for it); checked at entry
     int tf, tr, ts;        // warp-specialised two-shot: threads that finish rows / reduce slices / scatter (multiples of 32)
+    int scatter_lead;      // ... rows the scattering warps may run ahead of the finishing warps of their CTA (0: unbounded)
     int full;              // ... 1: a row is exactly VPT * tf vectors, no bounds checks in the finishing warps
     int lead_push;         // two-shot: chunks by which the scatter runs ahead of the reduction (>= 1)
     int lead_reduce;       // two-shot: chunks by which the reduction runs ahead of the epilogue (>= 1)
@@ -195,6 +196,12 @@ struct ArParams {
     LocalState *st;
     int64_t rs_slot_bytes;   // two-shot: stride between the N scatter slots of a buffer
     int64_t ag_off;          // two-shot: offset of the gather area inside a buffer
+    // warp-specialised two-shot: every rank's gather area as mapped here, the distance between its two
+    // call-parity copies, and -- where the gather areas lie in symmetric memory behind one NVSwitch multicast
+    // address -- that address: one store then lands in every rank's gather area (nullptr: one store per rank)
+    char *ag_base[kMaxRanks];
+    int64_t ag_stride;
+    char *ag_mc;
     int64_t ts_stride;       // two-shot: bytes between buffer 0 and buffer 1
     int64_t os_off;          // one-shot: offset of buffer 0
     int64_t os_slot_bytes;   // one-shot: stride between slots; a buffer is N slots
@@ -503,10 +510,18 @@ __device__ __forceinline__ void ar_body(const ArParams &p, int vb, int nb, Epilo
 // others, which is what a single thread-set walking the three roles in lock step cannot do.  The
 // row reductions of the finishing warps use a named barrier of their own.
 template <typename T, int NR>
-__device__ __forceinline__ void ws_scatter(const ArParams &p, int64_t ts_off, int vb, int nb, int tid, int nthreads) {
+__device__ __forceinline__ void ws_scatter(const ArParams &p, int64_t ts_off, int vb, int nb, int tid, int nthreads,
+                                           const volatile int *rows_finished) {
     constexpr int U = NR == 2 ? 4 : (NR == 4 ? 2 : 1);   // slice vectors per thread and peer that travel together
     const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
-    for (int row = vb; row < p.rows; row += nb) {
+    int k = 0;
+    for (int row = vb; row < p.rows; row += nb, ++k) {
+        // Stay within `scatter_lead` rows of the finishing warps: what is pushed further ahead would wait in
+        // the peers' staging long enough to fall out of their L2 and come back from HBM.  The wait is on
+        // shared memory and bounded (a stalled finisher must not stop the scatter for good).
+        if (p.scatter_lead > 0) {
+            for (int spin = 0; k - *rows_finished > p.scatter_lead && spin < (1 << 16); ++spin) __nanosleep(100);
+        }
         const int len = row_len(p, row);
         const uint4 *src = in + static_cast<int64_t>(row) * p.row_vecs;
         const int64_t slot_row = static_cast<int64_t>(row) * p.vpr;
@@ -536,7 +551,7 @@ __device__ __forceinline__ void ws_scatter(const ArParams &p, int64_t ts_off, in
 }
 
 template <typename T, int NR>
-__device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int vb, int nb, int tid, int nthreads) {
+__device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int64_t ag_ts, int vb, int nb, int tid, int nthreads) {
     constexpr int U = NR == 2 ? 4 : (NR == 4 ? 2 : 1);   // slice vectors per thread in flight together: U * NR loads
     const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
     char *mine = p.peer_data[p.rank] + ts_off;
@@ -571,10 +586,15 @@ __device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int
                         }
                     }
                     const uint4 red = payload<T>(sum_in_rank_order<T, NR>(part[u]));
+                    if (p.ag_mc) {
+                        // the switch copies this one store into every rank's gather area, this rank's included
+                        multimem_st(reinterpret_cast<uint4 *>(p.ag_mc + ag_ts) + base + vl, red);
+                    } else {
 #pragma unroll
-                    for (int d = 0; d < NR; ++d) {
-                        const int j = (p.rank + d) % NR;   // start with myself, then fan out: spreads the links
-                        st_peer(reinterpret_cast<uint4 *>(p.peer_data[j] + ts_off + p.ag_off) + base + vl, red);
+                        for (int d = 0; d < NR; ++d) {
+                            const int j = (p.rank + d) % NR;   // start with myself, then fan out: spreads the links
+                            st_peer(reinterpret_cast<uint4 *>(p.ag_base[j] + ag_ts) + base + vl, red);
+                        }
                     }
                 }
             }
@@ -583,24 +603,50 @@ __device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int
 }
 
 template <typename T, int VPT, bool FUSED, bool FULL>
-__device__ __forceinline__ void ws_finish(const ArParams &p, int64_t ts_off, int vb, int nb, const Group &grp, EpilogueSmem &sm) {
+__device__ __forceinline__ void ws_finish(const ArParams &p, int64_t ag_ts, int vb, int nb, const Group &grp, EpilogueSmem &sm) {
+    // With up to two vectors per thread the loads of the NEXT row (first poll of the gathered row, residual)
+    // are issued before the current row's epilogue, so a row's arithmetic hides the next row's memory latency.
+    constexpr bool AHEAD = VPT <= 2;
     float static_scale = 1.f;
     if constexpr (FUSED) {
         if (p.ep.q.mode == kQuantStatic) static_scale = *p.ep.scale_out;
     }
-    uint4 *ag = reinterpret_cast<uint4 *>(p.peer_data[p.rank] + ts_off + p.ag_off);
-    int parity = 0;
+    uint4 *ag = reinterpret_cast<uint4 *>(p.ag_base[p.rank] + ag_ts);
+    int parity = 0, done = 0;
+    uint4 x[VPT], res[VPT], nx[AHEAD ? VPT : 1], nres[AHEAD ? VPT : 1];
+    auto issue = [&](int row, uint4 (&dx)[AHEAD ? VPT : 1], uint4 (&dres)[AHEAD ? VPT : 1]) {
+        if constexpr (AHEAD) {
+            const int len = row < p.rows ? row_len(p, row) : 0;
+            const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int v = grp.tid + i * grp.n;
+                const bool in = FULL ? row < p.rows : v < len;
+                dx[i] = in ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
+                if constexpr (FUSED) dres[i] = in ? ld_stream(reinterpret_cast<const uint4 *>(p.ep.residual) + base + v) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    if constexpr (AHEAD) issue(vb, nx, nres);
     for (int row = vb; row < p.rows; row += nb) {
         const int len = row_len(p, row);
         const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
         const RowSeg seg = RowSeg{0, len, 0, 1};
-        uint4 x[VPT], res[VPT];
+        if constexpr (AHEAD) {
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = grp.tid + i * grp.n;
-            x[i] = (FULL || v < len) ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < VPT; ++i) {
+                x[i] = nx[i];
+                res[i] = nres[i];
+            }
+            issue(row + nb, nx, nres);
+        } else {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int v = grp.tid + i * grp.n;
+                x[i] = (FULL || v < len) ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
+            }
+            if constexpr (FUSED) load_residual<T, VPT, FULL>(p.ep, seg, row, grp, res);
         }
-        if constexpr (FUSED) load_residual<T, VPT, FULL>(p.ep, seg, row, grp, res);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = grp.tid + i * grp.n;
@@ -619,6 +665,7 @@ __device__ __forceinline__ void ws_finish(const ArParams &p, int64_t ts_off, int
                 if (FULL || v < len) st_stream(reinterpret_cast<uint4 *>(p.out) + base + v, x[i]);
             }
         }
+        if (grp.tid == 0) *const_cast<volatile int *>(&sm.rows_finished) = ++done;
     }
 }
 
@@ -629,17 +676,19 @@ __device__ __forceinline__ void ar_ws_body(const ArParams &p, int vb, int nb, Ep
         return;
     }
     begin_call(p.st, nb, sm);
+    if (threadIdx.x == 0) sm.rows_finished = 0;
     __syncthreads();
     const int64_t ts_off = static_cast<int64_t>(sm.seq & 1ull) * p.ts_stride;
+    const int64_t ag_ts = static_cast<int64_t>(sm.seq & 1ull) * p.ag_stride;
     const int tid = threadIdx.x;
     if (tid < p.tf) {
         const Group grp{tid, p.tf, 1};
-        if (p.full) ws_finish<T, VPT, FUSED, true>(p, ts_off, vb, nb, grp, sm);
-        else ws_finish<T, VPT, FUSED, false>(p, ts_off, vb, nb, grp, sm);
+        if (p.full) ws_finish<T, VPT, FUSED, true>(p, ag_ts, vb, nb, grp, sm);
+        else ws_finish<T, VPT, FUSED, false>(p, ag_ts, vb, nb, grp, sm);
     } else if (tid < p.tf + p.tr) {
-        ws_reduce<T, NR>(p, ts_off, vb, nb, tid - p.tf, p.tr);
+        ws_reduce<T, NR>(p, ts_off, ag_ts, vb, nb, tid - p.tf, p.tr);
     } else {
-        ws_scatter<T, NR>(p, ts_off, vb, nb, tid - p.tf - p.tr, p.ts);
+        ws_scatter<T, NR>(p, ts_off, vb, nb, tid - p.tf - p.tr, p.ts, &sm.rows_finished);
     }
 }
 

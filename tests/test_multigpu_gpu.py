@@ -120,6 +120,38 @@ def test_single_process_exchange_through_symmetric_memory(world):
         g.close()
 
 
+def _check_benchmark_config(g, key, world, sample_every):
+    """One call on real GPUs with the benchmark's own seeded inputs: residual_out must equal
+    T(T1 sum + residual) on ALL rows bit for bit, FP8 codes and scales are compared with the oracle
+    on every `sample_every`-th row, and all ranks must hold identical bytes."""
+    from gpuk_b200 import workloads as oin
+    cfg = oin.CONFIGS[key]
+    parts, res, w = oin.make_case(cfg, world)
+    outs = g.fused(parts, res, w, cfg.eps, cfg.quant_type, cfg.static_scale)
+    total = eo.allreduce_t1(parts)
+    want_res = total + res
+    for r, got in enumerate(outs):
+        assert torch.equal(got[0].view(torch.int16), want_res.view(torch.int16)), (key, world, r)
+        assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8)), (key, world, r)
+    idx = torch.arange(0, cfg.tokens, sample_every)
+    want = eo.add_rms_quant(total[idx], res[idx], w, cfg.eps, cfg.quant_type, cfg.static_scale)
+    got = outs[world - 1]
+    util.check_against_oracle((got[0][idx], got[1][idx], got[2][idx] if cfg.quant_type != 4 else got[2]), want, cfg.quant_type)
+
+
+@needs2
+@pytest.mark.parametrize("world", sorted({2, max(_worlds())}))
+def test_benchmark_configs_with_their_own_seeds_on_real_gpus(world):
+    """Configs 2, 3 and 5 in full and config 4 (16384 x 7168, 0.1 % outliers x 20) in full: the shapes, seeds
+    and distributions bench.py times, here with their results checked."""
+    g = PeerGroup(world, max_bytes=224 << 20)
+    try:
+        for key, every in (("c2", 1), ("c5", 1), ("c3", 1), ("c4", 16)):
+            _check_benchmark_config(g, key, world, every)
+    finally:
+        g.close()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -195,6 +227,87 @@ def _ipc_worker(rank, world, port, cases, q):
         env.barrier()
         del env
         dist.destroy_process_group()
+
+
+def _graph_worker(rank, world, port, q):
+    """Two fused calls captured into one CUDA graph through GPUKDistEnv, replayed on new data."""
+    import torch.distributed as dist
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    import gpuk_b200
+    # the two-shot gather goes through the NVSwitch multicast address where the fabric has one (asked for
+    # explicitly: by default it is used from four ranks)
+    env = gpuk_b200.GPUKDistEnv(group=None, device_id=rank, max_size_in_bytes=64 << 20, gather_multicast=True)
+    failures = []
+    try:
+        shapes = [(8, 8192), (300, 8192)]        # one-shot over a cluster, two-shot
+        x = [torch.zeros(t, h, dtype=torch.bfloat16, device="cuda") for t, h in shapes]
+        r = [torch.zeros(t, h, dtype=torch.bfloat16, device="cuda") for t, h in shapes]
+        w = [torch.ones(h, dtype=torch.bfloat16, device="cuda") for _, h in shapes]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for i in range(2):                   # warm-up outside the capture (both staging parities)
+                [env.allreduce_add_rms_fused(x[k], r[k], w[k], 1e-6, True) for k in range(2)]
+            torch.cuda.synchronize()
+            env.barrier()
+            with env.capture():
+                with torch.cuda.graph(graph, stream=side):
+                    outs = [env.allreduce_add_rms_fused(x[k], r[k], w[k], 1e-6, True) for k in range(2)]
+        torch.cuda.current_stream().wait_stream(side)
+        for rep in range(3):
+            cases = [util.random_case(world, t, h, torch.bfloat16, seed=5000 + 10 * rep + k) for k, (t, h) in enumerate(shapes)]
+            for k, (parts, res, wt) in enumerate(cases):
+                x[k].copy_(parts[rank])
+                r[k].copy_(res)
+                w[k].copy_(wt)
+            torch.cuda.synchronize()
+            env.barrier()
+            graph.replay()
+            if rep == 1:
+                graph.replay()      # twice on the same data: the device-side call counter must still be in step
+            torch.cuda.synchronize()
+            for k, (parts, res, wt) in enumerate(cases):
+                want = eo.epilogue_t1(parts, res, wt, 1e-6, 3)
+                got = tuple(t.cpu() for t in outs[k])
+                try:
+                    util.check_against_oracle(got, want, 3)
+                except AssertionError as e:   # pragma: no cover
+                    failures.append(f"replay {rep} shape {shapes[k]}: {e}")
+        try:
+            env.check()
+        except RuntimeError as e:   # pragma: no cover
+            failures.append(str(e))
+    finally:
+        q.put((rank, failures))
+        env.barrier()
+        del env
+        dist.destroy_process_group()
+
+
+@needs2
+@pytest.mark.parametrize("world", sorted({2, max(_worlds())}))
+def test_cuda_graph_replay_across_ranks_follows_new_data(world):
+    """The registration-free design rests on this: a graph that holds fused calls of several ranks can be
+    replayed any number of times and stays in step, because the call counter lives on the device
+    (the reference registers and IPC-maps captured inputs instead, all_reduce_fusion.cpp:105-137, 168-233;
+    gpuk/__init__.py:98-129)."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_graph_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+    for rank, failures in results:
+        assert not failures, (rank, failures)
+    assert all(p.exitcode == 0 for p in procs)
 
 
 @needs2

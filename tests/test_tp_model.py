@@ -97,18 +97,31 @@ def _gpu_worker(rank, world, port, q):
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
                             device_id=torch.device("cuda", rank))
     import gpuk_b200
-    env = gpuk_b200.GPUKDistEnv(group=None, device_id=rank, max_size_in_bytes=16 << 20)
+    env = _RecordingEnv(gpuk_b200.GPUKDistEnv(group=None, device_id=rank, max_size_in_bytes=16 << 20))
     failures = []
+
+    def gather(p):
+        parts = [torch.empty_like(p) for _ in range(world)]
+        dist.all_gather(parts, p)
+        return parts
+
     try:
         args = DecoderArgs(**MID)
         tokens = torch.randint(0, args.vocab_size, (4, 1), generator=torch.Generator().manual_seed(3)).cuda()
         for fp8 in (False, True):
             logits = []
             for fused in (True, False):
+                env.calls.clear()
                 m = TPDecoder(args, env, device=f"cuda:{rank}", fused=fused, fp8=fp8, max_batch=4)
                 m.fill_kv_cache(128)
                 pos = torch.tensor([128], device=f"cuda:{rank}")
                 logits.append(m.forward(tokens, pos, cache_len=129).float())
+                if fused:
+                    torch.cuda.synchronize()
+                    try:
+                        _check_hand_offs(env.calls, gather)
+                    except AssertionError as e:   # pragma: no cover
+                        failures.append(f"fp8={fp8}: hand-off parity: {e}")
             torch.cuda.synchronize()
             err = (logits[0] - logits[1]).abs().max().item()
             ref = logits[1].abs().max().item()
@@ -139,6 +152,58 @@ def test_fused_decoder_matches_unfused_on_two_gpus():
         p.join(timeout=120)
     for rank, failures in results:
         assert not failures, (rank, failures)
+
+
+class _RecordingEnv:
+    """Wraps a GPUKDistEnv and keeps inputs and results of every fused hand-off the decoder makes."""
+
+    def __init__(self, env):
+        self._env = env
+        self.calls = []
+
+    def __getattr__(self, name):
+        return getattr(self._env, name)
+
+    def allreduce_add_rms_fused(self, partial, h, weight, eps, fp8_out=False, **kw):
+        p, r = partial.clone(), h.clone()
+        out = self._env.allreduce_add_rms_fused(partial, h, weight, eps, fp8_out, **kw)
+        self.calls.append((p, r, weight, eps, fp8_out, tuple(t.clone() for t in out)))
+        return out
+
+
+def _check_hand_offs(calls, gather):
+    """Every recorded hand-off against the oracle with the parity bars of the operator itself (so a wrong
+    scale on a single row of a single layer fails, which a tolerance on the logits would not notice)."""
+    from oracle import epilogue_oracle as eo
+    from tests import util
+    assert calls
+    for p, r, weight, eps, fp8_out, out in calls:
+        parts = [t.cpu() for t in gather(p)]
+        quant = 3 if fp8_out else 0
+        want = eo.epilogue_t1(parts, r.cpu(), weight.cpu(), eps, quant)
+        got = (out[0].cpu(), out[1].cpu(), out[2].cpu() if fp8_out else None)
+        util.check_against_oracle(got, want, quant)
+
+
+@pytest.mark.gpu
+def test_every_fused_hand_off_of_the_decoder_meets_the_operator_parity_bars_on_one_gpu():
+    import torch.distributed as dist
+    import gpuk_b200
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(_free_port()))
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    env = _RecordingEnv(gpuk_b200.GPUKDistEnv(group=None, device_id=0))
+    args = DecoderArgs(**MID)
+    tokens = torch.randint(0, args.vocab_size, (4, 1), generator=torch.Generator().manual_seed(3)).cuda()
+    for fp8 in (False, True):
+        env.calls.clear()
+        m = TPDecoder(args, env, device="cuda:0", fused=True, fp8=fp8, max_batch=4)
+        m.fill_kv_cache(128)
+        m.forward(tokens, torch.tensor([128], device="cuda:0"), cache_len=129)
+        torch.cuda.synchronize()
+        assert len(env.calls) >= 2 * args.n_layers
+        _check_hand_offs(env.calls, lambda p: [p])
 
 
 @pytest.mark.gpu
