@@ -75,17 +75,21 @@ def measured_hbm_peak():
 
 
 def dram_traffic(kernel, tokens, hidden):
-    """DRAM bytes per launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum) from the capture
-    table in profiles/dram_traffic.txt, scaled from the captured case to `tokens` x `hidden`
-    (traffic grows in proportion to the elements).  None when the table has no row for the kernel."""
+    """DRAM bytes per launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum) from the capture table in
+    profiles/dram_traffic.txt: the captured case of `kernel` whose shape is nearest to `tokens` x `hidden`, scaled
+    by the number of elements (traffic grows in proportion to them).  None when the table has no row for the kernel."""
+    best = None
     try:
         for line in open(os.path.join(ROOT, "profiles", "dram_traffic.txt")):
             f = line.split()
             if len(f) >= 4 and not line.startswith("#") and f[0] == kernel:
-                return float(f[3]) * (tokens * hidden) / (float(f[1]) * float(f[2]))
+                elems = float(f[1]) * float(f[2])
+                dist = abs(math.log(elems / (tokens * hidden)))
+                if best is None or dist < best[0]:
+                    best = (dist, float(f[3]) * (tokens * hidden) / elems)
     except Exception:
-        pass
-    return None
+        return None
+    return best[1] if best else None
 
 
 def hbm_bytes(tokens, hidden):

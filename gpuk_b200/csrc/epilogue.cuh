@@ -24,6 +24,8 @@
 // correctly rounded quotient.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace gpuk {
@@ -173,25 +175,30 @@ __device__ __forceinline__ void row_epilogue(const EpilogueArgs &a, const RowSeg
     const f32x2 y2 = f2_splat(y);
     const f32x2 neg_s2 = f2_splat(a.q.fnuz ? -0.5f * scale : -scale);
     uint8_t *qo = reinterpret_cast<uint8_t *>(a.norm_out) + (row_base + vbase) * KV;
+    auto quantise = [&](auto fnuz_tag) {
+        constexpr bool FNUZ = decltype(fnuz_tag)::value;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        f32x2 p[NP];
-        Elem<T>::unpack2(x[i], p);
-        uint32_t out[NP / 2];
+        for (int i = 0; i < VPT; ++i) {
+            f32x2 p[NP];
+            Elem<T>::unpack2(x[i], p);
+            uint32_t out[NP / 2];
 #pragma unroll
-        for (int k = 0; k < NP; k += 2) {
-            f32x2 q0 = f2_mul(p[k], y2), q1 = f2_mul(p[k + 1], y2);
-            q0 = f2_fma(f2_fma(q0, neg_s2, p[k]), y2, q0);
-            q1 = f2_fma(f2_fma(q1, neg_s2, p[k + 1]), y2, q1);
-            uint32_t w = (cvt_e4m3x4_pairs(q0, q1) & 0x7f7f7f7fu) | Elem<T>::sign_bytes(x[i], k / 2);
-            out[k / 2] = a.q.fnuz ? fold_negative_zero_bytes(w) : w;
+            for (int k = 0; k < NP; k += 2) {
+                f32x2 q0 = f2_mul(p[k], y2), q1 = f2_mul(p[k + 1], y2);
+                q0 = f2_fma(f2_fma(q0, neg_s2, p[k]), y2, q0);
+                q1 = f2_fma(f2_fma(q1, neg_s2, p[k + 1]), y2, q1);
+                const uint32_t w = (cvt_e4m3x4_pairs(q0, q1) & 0x7f7f7f7fu) | Elem<T>::sign_bytes(x[i], k / 2);
+                out[k / 2] = FNUZ ? fold_negative_zero_bytes(w) : w;
+            }
+            if (inside(i)) {
+                uint8_t *dst = qo + static_cast<size_t>(i) * grp.n * KV;
+                if constexpr (KV == 8) __stcs(reinterpret_cast<uint2 *>(dst), make_uint2(out[0], out[1]));
+                else __stcs(reinterpret_cast<uint32_t *>(dst), out[0]);
+            }
         }
-        if (inside(i)) {
-            uint8_t *dst = qo + static_cast<size_t>(i) * grp.n * KV;
-            if constexpr (KV == 8) __stcs(reinterpret_cast<uint2 *>(dst), make_uint2(out[0], out[1]));
-            else __stcs(reinterpret_cast<uint32_t *>(dst), out[0]);
-        }
-    }
+    };
+    if (a.q.fnuz) quantise(std::true_type());
+    else quantise(std::false_type());
 }
 
 }  // namespace gpuk
