@@ -88,13 +88,18 @@ def build_torch(verbose: bool = False, force: bool = False) -> str:
     return TORCH_LIB
 
 
-def build_oracle_ref(verbose: bool = False, ref: str = "/root/reference") -> str | None:
-    """Compile the reference's software FP8 cast into oracle/_ref (only where the reference is present)."""
-    mk = os.path.join(ROOT, "oracle", "ref_fp8")
-    if not os.path.isdir(ref) or not os.path.isdir(mk):
+def build_oracle_ref(verbose: bool = False, ref: str | None = None) -> str | None:
+    """Compile the reference's software FP8 cast and its fused CUDA kernels into oracle/_ref, from the
+    reference checkout named by `ref` or the environment variable GPUK_REFERENCE_DIR (skipped where none is given
+    or present: the built files travel with the tree)."""
+    ref = ref or os.environ.get("GPUK_REFERENCE_DIR")
+    if not ref or not os.path.isdir(ref):
         return None
-    _run(["make", "-C", mk, f"REF={ref}"], verbose)
-    return os.path.join(ROOT, "oracle", "_ref", "libref_fp8.so")
+    for sub in ("ref_fp8", "ref_kernels"):
+        mk = os.path.join(ROOT, "oracle", sub)
+        if os.path.isdir(mk):
+            _run(["make", "-C", mk, f"REF={ref}"], verbose)
+    return os.path.join(ROOT, "oracle", "_ref")
 
 
 def main(argv):

@@ -2,7 +2,7 @@
 
 Run where a checkout of the reference project is available (``--ref`` names its directory):
 
-    python tests/golden/make_golden.py [--ref <reference checkout>]
+    python tests/golden/make_golden.py --ref <reference checkout>
 
 The reference module ``gpuk/__init__.py`` loads a CUDA library at import time and binds
 ``torch.ops.gpuk.*`` names (``gpuk/__init__.py:10-35``).  Neither is needed for
@@ -128,7 +128,8 @@ def worker(rank, world, port, ref_root, case, out_dir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("GPUK_REFERENCE_DIR"), required=not os.environ.get("GPUK_REFERENCE_DIR"),
+                    help="directory of the reference checkout (or set GPUK_REFERENCE_DIR)")
     ap.add_argument("--out", default=HERE)
     ap.add_argument("--only", default=None, help="generate only the cases whose name contains this text")
     args = ap.parse_args()
