@@ -742,6 +742,87 @@ def reference_gpu_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_overlap(cfg, env, gpuk, rank, world, steps, barrier, gemm_k=3584):
+    """The step before the path (model/tensor_parallel.py:112-123): the row-parallel GEMM that produces the
+    partial sums, then the fused exchange.  Serial = one GEMM over all rows, then the exchange, on one stream (the
+    reference arrangement).  Overlapped = the exchange is launched first, confined to `sms` SMs, and reads a row
+    block only once its ready word is set; the GEMM runs block by block on a second stream and sets the word
+    behind each block.  Microseconds per step (GEMM + exchange), max over ranks."""
+    oin = load_workloads()
+    device = torch.device("cuda", torch.cuda.current_device())
+    tokens, hidden = cfg.tokens, cfg.hidden
+    g = torch.Generator().manual_seed(77 + rank)
+    a = (torch.randn(tokens, gemm_k, generator=g) / math.sqrt(gemm_k)).to(torch.bfloat16).to(device)
+    wmat = torch.randn(gemm_k, hidden, generator=torch.Generator().manual_seed(78)).to(torch.bfloat16).to(device)
+    res = oin.make_residual(cfg).to(device)
+    w = oin.make_weight(cfg).to(device)
+    partial = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device)
+    res_out = torch.empty_like(partial)
+    norm_out = torch.empty(partial.shape, dtype=torch.float8_e4m3fn, device=device)
+    scale = torch.empty(tokens, 1, dtype=torch.float32, device=device)
+    fptr = env.fptr or 0
+    prod = torch.cuda.Stream(device=device)
+    out = {"workload": cfg.name, "gemm": f"[{tokens}, {gemm_k}] x [{gemm_k}, {hidden}] bf16 (torch.matmul, a library GEMM)", "variants": []}
+
+    def serial(_):
+        torch.matmul(a, wmat, out=partial)
+        gpuk.allreduce_rms(fptr, partial, res, w, res_out, norm_out, scale, cfg.eps, cfg.quant_type)
+
+    def gemm_only(_):
+        torch.matmul(a, wmat, out=partial)
+
+    def exchange_only(_):
+        gpuk.allreduce_rms(fptr, partial, res, w, res_out, norm_out, scale, cfg.eps, cfg.quant_type)
+
+    env.set_option("ws_max_ctas", 0)
+    for name, fn in (("gemm_us", gemm_only), ("exchange_us", exchange_only), ("serial_us", serial)):
+        secs, _ = time_calls(fn, 1, steps, 3, barrier, world, min_seconds=0.0)
+        out[name] = secs / steps * 1e6
+    serial(0)
+    torch.cuda.synchronize()
+    want = (res_out.clone(), norm_out.clone(), scale.clone())
+    if not env.takes_ready_words(tokens, hidden):
+        out["overlap_unavailable"] = "this shape does not run the two-shot exchange with specialised warps"
+        return out
+    import ctypes
+    from gpuk_b200 import cabi
+    counter = [0]
+    for row_block, sms in ((2048, 48), (2048, 64), (1024, 64), (2048, 96)):
+        nblocks = -(-tokens // row_block)
+        words = torch.zeros(nblocks, dtype=torch.int32, device=device)
+        env.set_option("ws_max_ctas", sms)
+
+        def overlapped(_):
+            counter[0] += 1
+            v = counter[0]
+            cur = torch.cuda.current_stream()
+            prod.wait_stream(cur)
+            cabi.check(cabi.lib.gpuk_ws_set_ready_words(ctypes.c_void_p(env.fptr), ctypes.c_void_p(words.data_ptr()), row_block, v))
+            gpuk.allreduce_rms(fptr, partial, res, w, res_out, norm_out, scale, cfg.eps, cfg.quant_type)
+            with torch.cuda.stream(prod):
+                for i in range(nblocks):
+                    lo, hi = i * row_block, min((i + 1) * row_block, tokens)
+                    torch.matmul(a[lo:hi], wmat, out=partial[lo:hi])
+                    words[i:i + 1].fill_(v)
+            cur.wait_stream(prod)
+
+        counter[0] = 0
+        words.zero_()
+        torch.cuda.synchronize()
+        barrier()
+        secs, _ = time_calls(overlapped, 1, steps, 3, barrier, world, min_seconds=0.0)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(res_out.view(torch.int16), want[0].view(torch.int16)) and
+                    torch.equal(norm_out.view(torch.uint8), want[1].view(torch.uint8)) and torch.equal(scale, want[2]))
+        out["variants"].append({"row_block": row_block, "exchange_sms": sms, "overlapped_us": secs / steps * 1e6,
+                                "identical_to_serial": same})
+    env.set_option("ws_max_ctas", 0)
+    best = min(v["overlapped_us"] for v in out["variants"])
+    out["best_overlapped_us"] = best
+    out["speedup_vs_serial"] = out["serial_us"] / best
+    return out
+
+
 def run_crossover(env, gpuk, rank, world, barrier, hidden=8192):
     """Microseconds per call (CUDA graph replay of the rotating buffer sets) of the three exchanges over
     the token counts between decode and prefill; used to place the thresholds between them."""
@@ -850,6 +931,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-model", action="store_true", help="skip the decoder-model step (config 5) in the sweep")
     ap.add_argument("--crossover", action="store_true", help="also time one-shot / two-shot / symmetric over token counts")
+    ap.add_argument("--overlap", action="store_true",
+                    help="also time the producer GEMM + the exchange of the prefill shape, serial and overlapped through ready words")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="workspace tuning option for the exchange (gpuk_ws_set_option), e.g. two_shot_ws=0; repeatable")
     ap.add_argument("--case", choices=["norm_quant", "emulated"], help="run one short fixed case of a kernel and exit")
@@ -931,6 +1014,12 @@ def main():
                 sweep.append({"workload": "c5_decoder", "error": repr(e)[:300]})
 
     crossover = run_crossover(env, gpuk, rank, world, barrier) if (args.crossover and world > 1) else None
+    overlap = None
+    if args.overlap and world > 1:
+        try:
+            overlap = run_overlap(oin.CONFIGS["c4"], env, gpuk, rank, world, max(5, min(args.steps, 30)), barrier)
+        except Exception as e:
+            overlap = {"error": repr(e)[:300]}
 
     cpu = cpu_c1 = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -981,6 +1070,8 @@ def main():
         }
         if crossover is not None:
             line["crossover"] = crossover
+        if overlap is not None:
+            line["overlap"] = overlap
         print(json.dumps(line), flush=True)
     barrier()
     del env

@@ -306,16 +306,43 @@ class GPUKDistEnv:
         scale_out = torch.empty(allreduce_in.shape[0], 1, dtype=torch.float32, device=allreduce_in.device)
         return residual_out, norm_out, scale_out
 
+    def takes_ready_words(self, tokens: int, hidden: int, dtype: torch.dtype = torch.bfloat16) -> bool:
+        """True when a fused call of this shape can start before its input is complete (``ready=`` of
+        ``allreduce_add_rms_fused``): it must run the two-shot exchange with specialised warps."""
+        if not self.fptr:
+            return False
+        p = cabi.plan(self.world_size, tokens * hidden, hidden, cabi.dtype_code(dtype))
+        return bool(p.ws)
+
     def allreduce_add_rms_fused(self, allreduce_in, residual_in, rms_weight, eps, fp8_out=False, *,
-                                static_scale: Optional[torch.Tensor] = None, quant_type: Optional[int] = None):
+                                static_scale: Optional[torch.Tensor] = None, quant_type: Optional[int] = None,
+                                ready=None):
         """Fused all-reduce + residual add + RMSNorm (+ FP8), ``gpuk/__init__.py:175-205``.
 
         Returns ``(residual_out, norm_out, scale_out)`` like the reference.  With
         ``static_scale`` (a one-element fp32 CUDA tensor, or a float) the output is quantised
         with that single scale and ``scale_out`` is that tensor.
+
+        ``ready = (words, rows_per_word, value)`` lets the call start while ``allreduce_in`` is still being
+        written (by the row-parallel GEMM in front of it, ``model/tensor_parallel.py:117``): ``words`` is an int32
+        CUDA tensor, word i stands for rows ``[i * rows_per_word, (i + 1) * rows_per_word)`` and the kernel reads a row
+        only once its word is ``>= value``.  The producer stores the word after the rows, on any stream; the
+        fused call is then NOT ordered behind the producer by the caller.  Only for shapes for which
+        ``takes_ready_words`` is true; a producer that needs SMs while the exchange runs must be left room with
+        ``set_option("ws_max_ctas", n)``.  The reference has no counterpart.
         """
         self._require_workspace()
         self.capture_(allreduce_in)
+        if ready is not None:
+            import ctypes
+            words, rows_per_word, value = ready
+            if not self.fptr or words.dtype not in (torch.int32, torch.uint32) or not words.is_cuda:
+                raise RuntimeError("gpuk: ready words need a multi-rank environment and an int32 CUDA tensor")
+            need = -(-allreduce_in.shape[0] // int(rows_per_word))
+            if words.numel() < need:
+                raise RuntimeError(f"gpuk: {need} ready words needed, {words.numel()} given")
+            cabi.check(cabi.lib.gpuk_ws_set_ready_words(ctypes.c_void_p(self.fptr), ctypes.c_void_p(words.data_ptr()),
+                                                        int(rows_per_word), int(value)))
         residual_out = torch.empty_like(residual_in)
         if static_scale is not None:
             fp8_out = True

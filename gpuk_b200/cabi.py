@@ -67,6 +67,7 @@ _SIGNATURES = {
     "gpuk_ws_set_oneshot_max_bytes": (c_int, [_P, c_int64]),
     "gpuk_ws_set_option": (c_int, [_P, c_char_p, c_int64]),
     "gpuk_set_tuning": (c_int, [c_char_p, c_int64]),
+    "gpuk_ws_set_ready_words": (c_int, [_P, _P, c_int, c_uint32]),
     "gpuk_ws_set_timeout_ns": (c_int, [_P, c_uint64]),
     "gpuk_ws_status": (c_int, [_P, POINTER(c_uint32)]),
     "gpuk_ws_clear_status": (c_int, [_P]),

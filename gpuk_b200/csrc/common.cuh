@@ -51,7 +51,8 @@ struct LocalState {
 };
 
 // stage codes in status[3]
-enum Stage : int { kStageOneShot = 0, kStageScatter = 1, kStageGather = 2, kStageSelfTest = 3, kStageSymIn = 4, kStageSymOut = 5 };
+enum Stage : int { kStageOneShot = 0, kStageScatter = 1, kStageGather = 2, kStageSelfTest = 3, kStageSymIn = 4, kStageSymOut = 5,
+                   kStageReady = 6 };   // waiting for the producer of this rank's own input (row-block ready words)
 
 // kStatusClusterMismatch: the kernel found itself in a thread-block cluster of another size than the
 // host planned (status[6] = the size seen); it returns before it takes a ticket or writes anything.
@@ -652,6 +653,37 @@ static __device__ __noinline__ uint4 wait_landed_slow(const void *addr, uint4 v,
 }
 __device__ __forceinline__ uint4 wait_landed(const void *addr, uint4 v, LocalState *st, int rank, int stage, int peer) {
     return landed(v) ? v : wait_landed_slow(addr, v, st, rank, stage, peer);
+}
+
+// Row-block ready words of the local input: a producer on this GPU (the GEMM that writes the partial sums,
+// or a copy engine) stores `want` (or more) into a word after the rows it stands for are complete; the
+// acquire load orders this thread's later reads of those rows behind it.  Same bounds and reporting as
+// wait_landed; `peer` is this rank itself.  Returns false when it gave up.
+static __device__ __noinline__ bool wait_ready_slow(const uint32_t *word, uint32_t want, LocalState *st, int rank) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it <= kSpinCap; ++it) {
+        uint32_t seen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
+        if (seen >= want) return true;
+        if ((it & 63u) == 63u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+                if (ld_volatile_u32(&st->abort)) return false;
+            } else if (now - t0 > st->timeout_ns || ld_volatile_u32(&st->abort)) {
+                record_status(st, kStatusWaitTimeout, rank, blockIdx.x, kStageReady, rank, seen);
+                return false;
+            }
+        }
+        __nanosleep(100);
+    }
+    record_status(st, kStatusSpinCap, rank, blockIdx.x, kStageReady, rank, 0u);
+    return false;
+}
+__device__ __forceinline__ bool wait_ready(const uint32_t *word, uint32_t want, LocalState *st, int rank) {
+    uint32_t seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
+    return seen >= want ? true : wait_ready_slow(word, want, st, rank);
 }
 
 // Polls a flag until it has reached `want` (flags only grow), with the same bounds and the same

@@ -252,6 +252,10 @@ struct gpuk_ws {
     int64_t sym_cap = 0, sym_flag_off = 0;   // largest message; offset of the flags
     int64_t sym_min_bytes = 0;               // messages from this size take it (0: never automatically)
     bool sym_use_mc = true;                  // reduce inside the switch where a multicast mapping exists
+    const uint32_t *ready = nullptr;         // row-block ready words of the NEXT fused call's input (gpuk_ws_set_ready_words)
+    int ready_rows = 0;
+    uint32_t ready_value = 0;
+    int opt_ws_max_ctas = 0;                 // CTAs (= SMs) the warp-specialised kernel may take (0: all)
     bool gather_multicast = false;           // two-shot gather through the multicast address (symmetric memory holds the gather areas)
     std::map<uint32_t, int64_t> occupancy;   // CTAs resident on the whole GPU, by kernel instantiation
 };
@@ -636,6 +640,9 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     } else if (n == "ws_finish_threads" || n == "ws_reduce_threads" || n == "ws_scatter_threads") {
         if (value < 0 || value > 512 || value % 32) return fail(GPUK_ERR_INVALID_ARGUMENT, "%s must be a multiple of 32 in [0, 512]", name);
         (n == "ws_finish_threads" ? ws->opt_ws_tf : (n == "ws_reduce_threads" ? ws->opt_ws_tr : ws->opt_ws_ts)) = static_cast<int>(value);
+    } else if (n == "ws_max_ctas") {
+        if (value < 0 || value > kMaxBlocks) return fail(GPUK_ERR_INVALID_ARGUMENT, "ws_max_ctas must be in [0, %d]", kMaxBlocks);
+        ws->opt_ws_max_ctas = static_cast<int>(value);
     } else if (n == "ws_scatter_lead") {
         if (value < -1 || value > (1 << 20)) return fail(GPUK_ERR_INVALID_ARGUMENT, "ws_scatter_lead must be in [-1, 2^20]");
         ws->opt_ws_scatter_lead = static_cast<int>(value);
@@ -663,6 +670,15 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     } else {
         return fail(GPUK_ERR_INVALID_ARGUMENT, "unknown option '%s'", name);
     }
+    return GPUK_OK;
+}
+int gpuk_ws_set_ready_words(gpuk_ws *ws, const uint32_t *ready, int rows_per_word, uint32_t value) {
+    if (!ws) return fail(GPUK_ERR_INVALID_ARGUMENT, "null workspace");
+    if (ready && rows_per_word <= 0) return fail(GPUK_ERR_INVALID_ARGUMENT, "rows_per_word must be positive");
+    if (ready && (reinterpret_cast<uintptr_t>(ready) & 3u)) return fail(GPUK_ERR_INVALID_ARGUMENT, "ready words must be 4-byte aligned");
+    ws->ready = ready;
+    ws->ready_rows = ready ? rows_per_word : 0;
+    ws->ready_value = value;
     return GPUK_OK;
 }
 int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns) {
@@ -828,8 +844,14 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     p->rows_per_chunk = plan.rows_per_chunk;
     p->seg_vecs = (plan.row_vecs + plan.cluster - 1) / plan.cluster;
     p->cluster = plan.cluster;
+    if (ws->ready && !use_ws)
+        return fail(GPUK_ERR_UNSUPPORTED, "ready words need the two-shot exchange with specialised warps, which this call does not take "
+                                          "(message too small, rows shared by clusters, or switched off): order the call behind the producer instead");
     if (use_ws) {
-        plan.grid = plan.ws_grid;
+        plan.grid = ws->opt_ws_max_ctas > 0 ? std::min(plan.ws_grid, ws->opt_ws_max_ctas) : plan.ws_grid;
+        p->ready = ws->ready;
+        p->ready_rows = ws->ready_rows;
+        p->ready_value = ws->ready_value;
         plan.rows_per_chunk = 1;
         p->rows_per_chunk = 1;
         // rows the scatter may run ahead of the finish.  Measured at eight ranks with the multicast gather, 2 / 8 rows:
@@ -995,6 +1017,7 @@ static int run_ar(gpuk_ws *ws, const CallArgs &a, void *stream) {
     ArParams p;
     ArShape shape;
     int rc = build_ar_call(ws, a, 0, false, &p, &shape);
+    ws->ready = nullptr;      // ready words apply to one call
     if (rc) return rc;
     return by_dtype(a.dtype, [&](auto *t) {
         using T = std::remove_pointer_t<decltype(t)>;
@@ -1037,6 +1060,7 @@ int gpuk_emulated_allreduce_rms(gpuk_ws *const *wss, int world_size, void *const
                       numel, hidden, dtype, eps, quant_type};
         ArShape s;
         int rc = build_ar_call(ws, a, force_mode, true, &host_params[r], &s);
+        ws->ready = nullptr;      // ready words apply to one call
         if (rc) return rc;
         if (r == 0) shape = s;
         else if (s.grid != shape.grid || s.threads != shape.threads || s.vpt != shape.vpt || s.two_shot != shape.two_shot ||

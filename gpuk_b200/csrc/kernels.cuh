@@ -202,6 +202,12 @@ struct ArParams {
     char *ag_base[kMaxRanks];
     int64_t ag_stride;
     char *ag_mc;
+    // warp-specialised two-shot: the input may still be in the making.  Word row / ready_rows of `ready` reaches
+    // ready_value once those rows of `in` are complete; the scattering and reducing warps wait for it before they
+    // read a row (nullptr: the whole input is there when the kernel starts).
+    const uint32_t *ready;
+    int ready_rows;
+    uint32_t ready_value;
     int64_t ts_stride;       // two-shot: bytes between buffer 0 and buffer 1
     int64_t os_off;          // one-shot: offset of buffer 0
     int64_t os_slot_bytes;   // one-shot: stride between slots; a buffer is N slots
@@ -525,6 +531,7 @@ __device__ __forceinline__ void ws_scatter(const ArParams &p, int64_t ts_off, in
         const int len = row_len(p, row);
         const uint4 *src = in + static_cast<int64_t>(row) * p.row_vecs;
         const int64_t slot_row = static_cast<int64_t>(row) * p.vpr;
+        if (p.ready) wait_ready(p.ready + row / p.ready_rows, p.ready_value, p.st, p.rank);
         for (int v0 = tid; v0 < p.vpr; v0 += U * nthreads) {
             uint4 a[NR - 1][U];
 #pragma unroll
@@ -559,6 +566,7 @@ __device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int
         const int len = row_len(p, row);
         const int64_t base = static_cast<int64_t>(row) * p.row_vecs + p.rank * p.vpr;
         const int64_t slot_row = static_cast<int64_t>(row) * p.vpr;
+        if (p.ready) wait_ready(p.ready + row / p.ready_rows, p.ready_value, p.st, p.rank);   // this rank's own slice comes from `in`
         for (int v0 = tid; v0 < p.vpr; v0 += U * nthreads) {
             uint4 part[U][NR];
             bool have[U];

@@ -175,6 +175,24 @@ int gpuk_allreduce_rms(gpuk_ws *ws, const void *allreduce_in, const void *residu
                        int64_t numel, int hidden, int dtype, float eps, int quant_type, void *stream);
 
 /*
+ * The step before the path: the partial sums usually come out of the row-parallel GEMM
+ * (model/tensor_parallel.py:112-123, F.linear at :117), which the reference lets finish before its
+ * all-reduce starts.  Here the NEXT gpuk_allreduce_rms / gpuk_emulated_allreduce_rms call on `ws` may
+ * start while its input is still being produced: word i of `ready` (device memory of this GPU, 4-byte
+ * words) stands for rows [i * rows_per_word, (i + 1) * rows_per_word) of allreduce_in, and the kernel reads
+ * a row only after its word has reached `value` (unsigned compare, so a producer can count calls up and
+ * never reset the words).  The producer -- the epilogue of a row-block GEMM, a kernel behind it on its
+ * stream, or a copy engine -- stores the word after the rows are complete; blocks may complete in any order.
+ * Applies to one call and only where that call runs the two-shot exchange with specialised warps
+ * (gpuk_plan.ws == 1), otherwise the call fails with GPUK_ERR_UNSUPPORTED and the caller orders it behind the
+ * producer as usual.  A producer that needs SMs while the exchange runs must be given room: option
+ * "ws_max_ctas" caps the SMs the exchange occupies.  A word that never arrives ends in the same bounded wait and
+ * status report as a silent peer (stage 6).  ready = NULL clears a pending setting.
+ * No counterpart in the reference.
+ */
+int gpuk_ws_set_ready_words(gpuk_ws *ws, const uint32_t *ready, int rows_per_word, uint32_t value);
+
+/*
  * Replaces allreduce_inplace (src/register.cpp:33-34, all_reduce_fusion.cpp:340-361) and
  * allreduce_inplace_impl (impl.h:115-144): sum over ranks, fp32 accumulation in rank order,
  * one rounding, written back over `data`.  numel * element size must be a multiple of 16.
@@ -239,7 +257,11 @@ int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes);
  * Tuning options of the exchanges; all ranks must set the same values.  Names:
  * "rows_per_chunk" (rows a CTA takes through one pipeline role at a time, 0: default),
  * "ctas_per_sm" (cap on resident CTAs per SM, 0: default), "cluster" (CTAs of a thread-block
- * cluster that share a row: 1, 2, 4, 8, 0: default), "lead_push" / "lead_reduce" (pipeline
+ * cluster that share a row: 1, 2, 4, 8, 0: default), "two_shot_ws" (1: two-shot calls without clusters run the
+ * kernel with specialised warps, 0: the lock-step kernel), "ws_finish_threads" / "ws_reduce_threads" /
+ * "ws_scatter_threads" (its threads per role, 0: default), "ws_scatter_lead" (rows its scatter may run ahead of
+ * its finish, -1: default, 0: unbounded), "ws_max_ctas" (SMs it may occupy, 0: all), "gather_multicast" (1: its
+ * gather goes through the multicast address of the attached symmetric memory), "lead_push" / "lead_reduce" (pipeline
  * depths in chunks, 0: default), "oneshot_max_bytes", "sym_min_bytes" (smallest message that
  * takes the exchange through symmetric memory, 0: never), "sym_multicast" (1: reduce inside the
  * switch where a multicast mapping exists, 0: plain peer loads).  "test_withhold_cluster" = 1 is a
@@ -265,7 +287,7 @@ int gpuk_ws_set_timeout_ns(gpuk_ws *ws, uint64_t ns);
  * cluster of another size than planned (out[6] = the size seen; it then wrote nothing and the
  * call returns GPUK_ERR_BAD_LAUNCH), out[1] = rank, out[2] = CTA,
  * out[3] = stage (0 one-shot, 1 scatter, 2 gather, 3 self-test, 4 / 5 the two flags of the
- * exchange through symmetric memory), out[4] = peer whose data was
+ * exchange through symmetric memory, 6 a ready word of this rank's own input), out[4] = peer whose data was
  * awaited, out[5] = thread, out[6] = word seen.  Returns GPUK_ERR_PEER_TIMEOUT if out[0] != 0.
  * The reference spins forever instead (communicator.h:98-99).
  */

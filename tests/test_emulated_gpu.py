@@ -249,6 +249,94 @@ def test_two_shot_with_specialised_warps(world, tokens, hidden, quant, dtype):
                 assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8))
 
 
+def _emulated_call_async(g, parts, res, w, quant, outs):
+    import ctypes
+    from gpuk_b200 import cabi
+    ws = (ctypes.c_void_p * g.world)(*[h.value for h in g.ws])
+    cabi.check(cabi.lib.gpuk_emulated_allreduce_rms(
+        ws, g.world, g._arr(parts), util.ptr(res), util.ptr(w), g._arr([o[0] for o in outs]), g._arr([o[1] for o in outs]),
+        g._arr([o[2] for o in outs]), parts[0].numel(), parts[0].shape[-1], cabi.dtype_code(parts[0].dtype), 1e-6, quant,
+        TWO_SHOT, util.stream_ptr()))
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_input_produced_in_scrambled_row_blocks_while_the_exchange_runs(world):
+    """The step before the path (model/tensor_parallel.py:117): the exchange is launched while its input does
+    not exist yet.  Row blocks of every rank's partial arrive one by one, in a different scrambled order on
+    every rank, each followed by its ready word -- written by the copy engine from pinned memory, which needs
+    no SM (the waiting kernel holds them).  A kernel that read a row before its word would pick up the NaN
+    fill; results must be those of the oracle."""
+    import ctypes
+    from cuda.bindings import runtime as cudart  # noqa: F401  (imported before any kernel waits)
+    from gpuk_b200 import cabi
+    tokens, hidden, rows_per_word = 600, 2048, 64
+    nwords = -(-tokens // rows_per_word)
+    assert cabi.plan(world, tokens * hidden, hidden, oneshot_max_bytes=1).ws == 1
+    parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world + 4000)
+    want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
+    pinned = [p.pin_memory() for p in parts]
+    with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        g.set_option("ws_max_ctas", 16)        # the kernels of all emulated ranks leave some SMs of the one GPU free
+        for call in range(2):
+            value = call + 1                   # words count calls up, nothing is reset in between
+            d_parts = [torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+            if call == 0:
+                words = [torch.zeros(nwords, dtype=torch.int32, device="cuda") for _ in range(world)]
+            flag = torch.tensor([value], dtype=torch.int32).pin_memory()
+            d_res, d_w = res.cuda(), w.cuda()
+            outs = [util.alloc_outputs(p, 3) for p in d_parts]
+            # everything that allocates or creates (streams included: creating one can wait for the device to go
+            # idle) happens before the launch; after it only copies are enqueued
+            feeder = torch.cuda.Stream()
+            gen = torch.Generator().manual_seed(call)
+            orders = [torch.randperm(nwords, generator=gen).tolist() for _ in range(world)]
+            torch.cuda.synchronize()
+            for r in range(world):
+                cabi.check(cabi.lib.gpuk_ws_set_ready_words(g.ws[r], ctypes.c_void_p(words[r].data_ptr()), rows_per_word, value))
+            _emulated_call_async(g, d_parts, d_res, d_w, 3, outs)
+            for step in range(nwords):
+                for r in range(world):
+                    i = orders[r][step]
+                    lo, hi = i * rows_per_word, min((i + 1) * rows_per_word, tokens)
+                    util.h2d_async(d_parts[r][lo:hi], pinned[r][lo:hi], feeder)
+                    util.h2d_async(words[r][i:i + 1], flag, feeder)
+            torch.cuda.synchronize()
+            for r in range(world):
+                rc, st = g.status(r)
+                assert rc == 0, (r, st, cabi.last_error())
+            got = [(o[0].cpu(), o[1].cpu(), o[2].cpu()) for o in outs]
+            _check_all_ranks(got, want, 3)
+
+
+def test_ready_word_that_never_arrives_is_reported_and_ready_words_are_refused_where_they_cannot_work():
+    import ctypes
+    from gpuk_b200 import cabi
+    world, tokens, hidden = 2, 300, 2048
+    parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=9)
+    d_parts, d_res, d_w = [p.cuda() for p in parts], res.cuda(), w.cuda()
+    with util.EmulatedGroup(world, max_bytes=4 << 20) as g:
+        words = [torch.ones(5, dtype=torch.int32, device="cuda") for _ in range(world)]
+        words[1][3] = 0                                         # rows 192..255 of rank 1 never become ready
+        for r in range(world):
+            cabi.check(cabi.lib.gpuk_ws_set_timeout_ns(g.ws[r], 50_000_000))
+            cabi.check(cabi.lib.gpuk_ws_set_ready_words(g.ws[r], ctypes.c_void_p(words[r].data_ptr()), 64, 1))
+        outs = [util.alloc_outputs(p, 3) for p in d_parts]
+        _emulated_call_async(g, d_parts, d_res, d_w, 3, outs)
+        torch.cuda.synchronize()
+        rc, st = g.status(1)
+        assert rc == cabi.ERR_PEER_TIMEOUT and st[0] == 1 and st[1] == 1 and st[3] == 6, (rc, st)      # stage 6: a ready word
+        g.clear_status()
+        # ready words apply to one call: the next one runs without them and is correct
+        _check_all_ranks(g.fused(d_parts, d_res, d_w, 1e-6, 3, force_mode=TWO_SHOT), eo.epilogue_t1(parts, res, w, 1e-6, 3), 3)
+        # a call that takes the one-shot exchange cannot wait for ready words: refused, not ignored
+        small = util.random_case(world, 4, 2048, torch.bfloat16, seed=10)
+        for r in range(world):
+            cabi.check(cabi.lib.gpuk_ws_set_ready_words(g.ws[r], ctypes.c_void_p(words[r].data_ptr()), 64, 1))
+        with pytest.raises(cabi.GpukError) as e:
+            g.fused([p.cuda() for p in small[0]], small[1].cuda(), small[2].cuda(), 1e-6, 3)
+        assert e.value.status == cabi.ERR_UNSUPPORTED
+
+
 def test_prefill_distribution_with_outliers_eight_ranks():
     """Config 4's inputs (0.1 % of the partials multiplied by 20, seeds of the benchmark) at
     2048 of its 16384 rows, eight ranks, two-shot: more chunks than resident CTAs."""

@@ -152,6 +152,56 @@ def test_benchmark_configs_with_their_own_seeds_on_real_gpus(world):
         g.close()
 
 
+@needs2
+@pytest.mark.parametrize("world", sorted({2, max(_worlds())}))
+def test_exchange_starts_before_its_input_is_complete_on_real_gpus(world):
+    """Ready words over real NVLink: every rank's kernel is launched first, then the rows of its partial and
+    their ready words arrive block by block through the copy engine, in a different scrambled order per rank."""
+    from cuda.bindings import runtime as cudart  # noqa: F401  (imported before any kernel waits)
+    from gpuk_b200 import cabi
+    tokens, hidden, rows_per_word = 1200, 4096, 128
+    nwords = -(-tokens // rows_per_word)
+    parts, res, w = util.random_case(world, tokens, hidden, torch.bfloat16, seed=world + 77)
+    want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
+    pinned = [p.pin_memory() for p in parts]
+    flag = torch.tensor([1], dtype=torch.int32).pin_memory()
+    g = PeerGroup(world)
+    try:
+        dev = [(torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device=f"cuda:{r}"), res.cuda(r), w.cuda(r))
+               for r in range(world)]
+        words = [torch.zeros(nwords, dtype=torch.int32, device=f"cuda:{r}") for r in range(world)]
+        outs = [util.alloc_outputs(dev[r][0], 3) for r in range(world)]
+        # streams are created before the launches (creating one can wait for the device to go idle)
+        gen = torch.Generator().manual_seed(world)
+        orders = [torch.randperm(nwords, generator=gen).tolist() for _ in range(world)]
+        feeders = [torch.cuda.Stream(device=r) for r in range(world)]
+        for r in range(world):
+            torch.cuda.synchronize(r)
+        for r in range(world):
+            with torch.cuda.device(r):
+                x, rr, ww = dev[r]
+                cabi.check(cabi.lib.gpuk_ws_set_ready_words(g.ws[r], ctypes.c_void_p(words[r].data_ptr()), rows_per_word, 1))
+                cabi.check(cabi.lib.gpuk_allreduce_rms(
+                    g.ws[r], util.ptr(x), util.ptr(rr), util.ptr(ww), util.ptr(outs[r][0]), util.ptr(outs[r][1]), util.ptr(outs[r][2]),
+                    x.numel(), hidden, cabi.DTYPE_BF16, 1e-6, 3, ctypes.c_void_p(torch.cuda.current_stream(r).cuda_stream)))
+        for step in range(nwords):
+            for r in range(world):
+                i = orders[r][step]
+                lo, hi = i * rows_per_word, min((i + 1) * rows_per_word, tokens)
+                with torch.cuda.device(r):
+                    util.h2d_async(dev[r][0][lo:hi], pinned[r][lo:hi], feeders[r])
+                    util.h2d_async(words[r][i:i + 1], flag, feeders[r])
+        for r in range(world):
+            torch.cuda.synchronize(r)
+        for r in range(world):
+            out = (ctypes.c_uint32 * 8)()
+            assert cabi.lib.gpuk_ws_status(g.ws[r], out) == 0, list(out)
+            got = (outs[r][0].cpu(), outs[r][1].cpu(), outs[r][2].cpu())
+            util.check_against_oracle(got, want, 3)
+    finally:
+        g.close()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))

@@ -135,6 +135,18 @@ class EmulatedGroup:
         return [p.cpu() for p in parts]
 
 
+def h2d_async(dst: torch.Tensor, src_pinned: torch.Tensor, stream: torch.cuda.Stream) -> None:
+    """One cudaMemcpyAsync from pinned host memory on `stream`: a copy-engine transfer, whatever its size
+    (torch's copy_ turns a one-element host tensor into a fill kernel, which needs an SM)."""
+    from cuda.bindings import runtime as cudart
+    assert src_pinned.is_pinned() and dst.is_contiguous() and src_pinned.is_contiguous()
+    nbytes = dst.numel() * dst.element_size()
+    assert nbytes == src_pinned.numel() * src_pinned.element_size()
+    err, = cudart.cudaMemcpyAsync(dst.data_ptr(), src_pinned.data_ptr(), nbytes, cudart.cudaMemcpyKind.cudaMemcpyHostToDevice,
+                                  stream.cuda_stream)
+    assert err == cudart.cudaError_t.cudaSuccess, err
+
+
 def random_case(world, tokens, hidden, dtype, seed):
     g = torch.Generator().manual_seed(seed)
     parts = [torch.randn(tokens, hidden, generator=g).to(dtype) for _ in range(world)]
