@@ -26,6 +26,7 @@ Inputs are seeded synthetic tensors with the distributions of the baseline confi
 from __future__ import annotations
 
 import argparse
+import contextlib
 import importlib.util
 import json
 import math
@@ -778,18 +779,49 @@ def run_overlap(cfg, env, gpuk, rank, world, steps, barrier, gemm_k=3584):
     for name, fn in (("gemm_us", gemm_only), ("exchange_us", exchange_only), ("serial_us", serial)):
         secs, _ = time_calls(fn, 1, steps, 3, barrier, world, min_seconds=0.0)
         out[name] = secs / steps * 1e6
-    serial(0)
-    torch.cuda.synchronize()
-    want = (res_out.clone(), norm_out.clone(), scale.clone())
     if not env.takes_ready_words(tokens, hidden):
         out["overlap_unavailable"] = "this shape does not run the two-shot exchange with specialised warps"
         return out
     import ctypes
     from gpuk_b200 import cabi
     counter = [0]
-    for row_block, sms in ((2048, 48), (2048, 64), (1024, 64), (2048, 96)):
+    total_sms = torch.cuda.get_device_properties(device).multi_processor_count
+
+    class gemm_beside(object):
+        """The producer GEMMs of the overlapped step leave `sms` SMs to the exchange: cuBLASLt's SM-count target (PyTorch's
+        experimental carve-out).  Without it the library GEMM sizes its persistent grid for the whole GPU and runs in
+        two waves on what the exchange leaves free."""
+
+        def __init__(self, sms):
+            self.sms = sms
+
+        def __enter__(self):
+            self.lib = torch.backends.cuda.preferred_blas_library()
+            torch.backends.cuda.preferred_blas_library("cublaslt")
+            torch._C._set_sm_carveout_experimental(self.sms)
+
+        def __exit__(self, *exc):
+            torch._C._set_sm_carveout_experimental(None)
+            torch.backends.cuda.preferred_blas_library(self.lib)
+
+    have_carveout = hasattr(torch._C, "_set_sm_carveout_experimental")
+    confine = gemm_beside if have_carveout else (lambda sms: contextlib.nullcontext())
+    out["gemm_confined"] = (f"cuBLASLt SM-count target = {total_sms} - exchange SMs" if have_carveout
+                            else "not available in this PyTorch: the GEMM sizes its grid for the whole GPU")
+    for row_block, sms in ((2048, 16), (2048, 24), (2048, 32), (4096, 24), (2048, 48)):
         nblocks = -(-tokens // row_block)
         words = torch.zeros(nblocks, dtype=torch.int32, device=device)
+        # the same block GEMMs followed by the exchange, in stream order: the results the overlapped run must reproduce
+        env.set_option("ws_max_ctas", 0)
+
+        def blocks_then_exchange(_):
+            for i in range(nblocks):
+                lo, hi = i * row_block, min((i + 1) * row_block, tokens)
+                torch.matmul(a[lo:hi], wmat, out=partial[lo:hi])
+            gpuk.allreduce_rms(fptr, partial, res, w, res_out, norm_out, scale, cfg.eps, cfg.quant_type)
+
+        secs_b, _ = time_calls(blocks_then_exchange, 1, steps, 3, barrier, world, min_seconds=0.0)
+        torch.cuda.synchronize()
         env.set_option("ws_max_ctas", sms)
 
         def overlapped(_):
@@ -799,7 +831,7 @@ def run_overlap(cfg, env, gpuk, rank, world, steps, barrier, gemm_k=3584):
             prod.wait_stream(cur)
             cabi.check(cabi.lib.gpuk_ws_set_ready_words(ctypes.c_void_p(env.fptr), ctypes.c_void_p(words.data_ptr()), row_block, v))
             gpuk.allreduce_rms(fptr, partial, res, w, res_out, norm_out, scale, cfg.eps, cfg.quant_type)
-            with torch.cuda.stream(prod):
+            with torch.cuda.stream(prod), confine(sms):
                 for i in range(nblocks):
                     lo, hi = i * row_block, min((i + 1) * row_block, tokens)
                     torch.matmul(a[lo:hi], wmat, out=partial[lo:hi])
@@ -808,14 +840,35 @@ def run_overlap(cfg, env, gpuk, rank, world, steps, barrier, gemm_k=3584):
 
         counter[0] = 0
         words.zero_()
+        # Every kernel the producer will launch runs once, on its stream, while nothing waits for it.  With lazy module
+        # loading (the CUDA default) the first launch of a kernel loads it, and that load can wait for the device to
+        # go idle -- behind an exchange kernel that waits for this very producer.  The dry run uses the same shapes and
+        # a non-zero word value (a zero fill may take another kernel); the words are cleared again afterwards.
+        with torch.cuda.stream(prod), confine(sms):
+            for i in range(nblocks):
+                lo, hi = i * row_block, min((i + 1) * row_block, tokens)
+                torch.matmul(a[lo:hi], wmat, out=partial[lo:hi])
+                words[i:i + 1].fill_(1)
+        torch.cuda.synchronize()
+        confined_partial = partial.clone()      # the confined GEMM may pick another kernel: its own results are the reference
+        words.zero_()
         torch.cuda.synchronize()
         barrier()
         secs, _ = time_calls(overlapped, 1, steps, 3, barrier, world, min_seconds=0.0)
         torch.cuda.synchronize()
-        same = bool(torch.equal(res_out.view(torch.int16), want[0].view(torch.int16)) and
-                    torch.equal(norm_out.view(torch.uint8), want[1].view(torch.uint8)) and torch.equal(scale, want[2]))
+        env.check()      # a ready word that did not arrive in time would have been reported here
+        got = (res_out.clone(), norm_out.clone(), scale.clone())
+        gemm_same = bool(torch.equal(partial.view(torch.int16), confined_partial.view(torch.int16)))
+        # the exchange once more, in stream order, on the partial sums the overlapped step left behind
+        env.set_option("ws_max_ctas", 0)
+        barrier()
+        exchange_only(0)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(res_out.view(torch.int16), got[0].view(torch.int16)) and
+                    torch.equal(norm_out.view(torch.uint8), got[1].view(torch.uint8)) and torch.equal(scale, got[2]))
         out["variants"].append({"row_block": row_block, "exchange_sms": sms, "overlapped_us": secs / steps * 1e6,
-                                "identical_to_serial": same})
+                                "block_gemms_then_exchange_us": secs_b / steps * 1e6,
+                                "identical_to_exchange_in_stream_order": same, "gemm_output_reproducible": gemm_same})
     env.set_option("ws_max_ctas", 0)
     best = min(v["overlapped_us"] for v in out["variants"])
     out["best_overlapped_us"] = best

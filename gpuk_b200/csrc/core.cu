@@ -245,6 +245,7 @@ struct gpuk_ws {
     int opt_ws_scatter_lead = -1;        // rows its scatter may run ahead of its finish (-1: default, 0: unbounded)
     int opt_ws_tf = 0, opt_ws_tr = 0, opt_ws_ts = 0;   // threads per role of that kernel (0: default)
     int opt_two_shot_ws = 1;             // 1: two-shot calls without clusters run the warp-specialised kernel
+    int opt_two_rank_one_hop = 1;        // 1: at two ranks that kernel sends whole rows to the peer (one hop) instead of slices (two)
     bool test_withhold_cluster = false;  // test hook: launch without the planned cluster attribute
     // exchange through symmetric memory (gpuk_ws_attach_symmetric)
     char *sym[kMaxRanks] = {};
@@ -637,6 +638,9 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value) {
     } else if (n == "two_shot_ws") {
         if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "two_shot_ws must be 0 or 1");
         ws->opt_two_shot_ws = static_cast<int>(value);
+    } else if (n == "two_rank_one_hop") {
+        if (value != 0 && value != 1) return fail(GPUK_ERR_INVALID_ARGUMENT, "two_rank_one_hop must be 0 or 1");
+        ws->opt_two_rank_one_hop = static_cast<int>(value);
     } else if (n == "ws_finish_threads" || n == "ws_reduce_threads" || n == "ws_scatter_threads") {
         if (value < 0 || value > 512 || value % 32) return fail(GPUK_ERR_INVALID_ARGUMENT, "%s must be a multiple of 32 in [0, 512]", name);
         (n == "ws_finish_threads" ? ws->opt_ws_tf : (n == "ws_reduce_threads" ? ws->opt_ws_tr : ws->opt_ws_ts)) = static_cast<int>(value);
@@ -869,6 +873,17 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         p->ts = plan.ws_ts;
         // no bounds checks in the finishing warps when every row, the last included, fills the tile
         p->full = (plan.row_vecs == plan.ws_vpt * plan.ws_tf && p->total_vecs % plan.row_vecs == 0) ? 1 : 0;
+        // Two ranks: whole rows straight into the peer's gather area, one hop.  The finishing warps then read this
+        // rank's input themselves, so the outputs must not overlap it (a finished row would overwrite input that has
+        // not been pushed yet), and an input still in the making (ready words) keeps the two-hop exchange, whose
+        // finishing warps never touch the input.
+        auto overlaps_in = [&](const void *q, int64_t bytes) {
+            const char *b = static_cast<const char *>(q), *i0 = static_cast<const char *>(a.in);
+            return q && b < i0 + plan.message_bytes && i0 < b + bytes;
+        };
+        p->one_hop = (ws->world == 2 && fused && ws->opt_two_rank_one_hop && !ws->ready &&
+                      !overlaps_in(a.residual_out, plan.message_bytes) && !overlaps_in(a.norm_out, plan.message_bytes)) ? 1 : 0;
+        if (p->one_hop) p->ts = kWs1PushThreads, p->tr = 0;
     }
     p->lead_push = std::max(1, ws->opt_lead_push > 0 ? ws->opt_lead_push : plan.lead_push);
     p->lead_reduce = std::max(1, ws->opt_lead_reduce > 0 ? ws->opt_lead_reduce : plan.lead_reduce);
@@ -896,14 +911,14 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
     shape->vpt = use_ws ? plan.ws_vpt : plan.vpt;
     shape->two_shot = !one_shot;
     shape->fused = fused;
-    shape->ws = use_ws ? 1 : 0;
-    shape->threads = use_ws ? plan.ws_tf + plan.ws_tr + plan.ws_ts : plan.threads;
+    shape->ws = use_ws ? (p->one_hop ? 2 : 1) : 0;
+    shape->threads = use_ws ? p->tf + p->tr + p->ts : plan.threads;
     shape->cluster = plan.cluster;
     shape->grid = plan.grid;
     shape->sym = sym;
     // the grid must be co-resident: CTAs of equal index on different ranks wait for each other
     const uint32_t key = static_cast<uint32_t>(a.dtype) | (shape->vpt << 4) | (one_shot ? 1u << 8 : 0u) |
-                         (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (use_ws ? 1u << 11 : 0u) |
+                         (fused ? 1u << 9 : 0u) | (emulated ? 1u << 10 : 0u) | (use_ws ? 1u << 11 : 0u) | (p->one_hop ? 1u << 30 : 0u) |
                          (static_cast<uint32_t>(shape->threads) << 12) |
                          (static_cast<uint32_t>(plan.cluster) << 24) | (static_cast<uint32_t>(sym) << 28);
     int64_t resident = 0;

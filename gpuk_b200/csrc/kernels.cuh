@@ -186,6 +186,8 @@ struct ArParams {
     int tf, tr, ts;        // warp-specialised two-shot: threads that finish rows / reduce slices / scatter (multiples of 32)
     int scatter_lead;      // ... rows the scattering warps may run ahead of the finishing warps of their CTA (0: unbounded)
     int full;              // ... 1: a row is exactly VPT * tf vectors, no bounds checks in the finishing warps
+    int one_hop;           // ... two ranks only, 1: whole rows go straight to the peer's gather area and the finishing warps add
+                           //     their own row: one NVLink hop instead of two for the same bytes on the wire
     int lead_push;         // two-shot: chunks by which the scatter runs ahead of the reduction (>= 1)
     int lead_reduce;       // two-shot: chunks by which the reduction runs ahead of the epilogue (>= 1)
     EpilogueArgs ep;       // fused only
@@ -557,6 +559,34 @@ __device__ __forceinline__ void ws_scatter(const ArParams &p, int64_t ts_off, in
     }
 }
 
+// Two ranks, one hop: the scattering threads push whole rows of this rank's input into the peer's gather area.
+// With two ranks a two-shot exchange sends half of every row twice (the peer's slice, then the reduced own slice)
+// and a whole row once is the same number of bytes, so the second hop and the slice reduction buy nothing.
+template <typename T>
+__device__ __forceinline__ void ws_push_rows(const ArParams &p, int64_t ag_ts, int vb, int nb, int tid, int nthreads,
+                                             const volatile int *rows_finished) {
+    constexpr int U = 4;
+    const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
+    uint4 *peer = reinterpret_cast<uint4 *>(p.ag_base[p.rank ^ 1] + ag_ts);
+    int k = 0;
+    for (int row = vb; row < p.rows; row += nb, ++k) {
+        if (p.scatter_lead > 0) {   // as in ws_scatter: what waits too long in the peer's staging falls out of its L2
+            for (int spin = 0; k - *rows_finished > p.scatter_lead && spin < (1 << 16); ++spin) __nanosleep(100);
+        }
+        const int len = row_len(p, row);
+        const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
+        for (int v0 = tid; v0 < len; v0 += U * nthreads) {
+            uint4 a[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (v0 + u * nthreads < len) a[u] = ld_stream(in + base + v0 + u * nthreads);
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (v0 + u * nthreads < len) st_peer(peer + base + v0 + u * nthreads, payload<T>(a[u]));
+        }
+    }
+}
+
 template <typename T, int NR>
 __device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int64_t ag_ts, int vb, int nb, int tid, int nthreads) {
     constexpr int U = NR == 2 ? 4 : (NR == 4 ? 2 : 1);   // slice vectors per thread in flight together: U * NR loads
@@ -610,32 +640,36 @@ __device__ __forceinline__ void ws_reduce(const ArParams &p, int64_t ts_off, int
     }
 }
 
-template <typename T, int VPT, bool FUSED, bool FULL>
+// OWN (two ranks, one hop): the gather area holds the peer's row, not the sum; this rank's own row is read from
+// its input and the two are added in rank order, in fp32, rounded once.
+template <typename T, int VPT, bool FUSED, bool FULL, bool OWN = false>
 __device__ __forceinline__ void ws_finish(const ArParams &p, int64_t ag_ts, int vb, int nb, const Group &grp, EpilogueSmem &sm) {
     // With up to two vectors per thread the loads of the NEXT row (first poll of the gathered row, residual)
     // are issued before the current row's epilogue, so a row's arithmetic hides the next row's memory latency.
     constexpr bool AHEAD = VPT <= 2;
+    const uint4 *in = reinterpret_cast<const uint4 *>(p.in);
     float static_scale = 1.f;
     if constexpr (FUSED) {
         if (p.ep.q.mode == kQuantStatic) static_scale = *p.ep.scale_out;
     }
     uint4 *ag = reinterpret_cast<uint4 *>(p.ag_base[p.rank] + ag_ts);
     int parity = 0, done = 0;
-    uint4 x[VPT], res[VPT], nx[AHEAD ? VPT : 1], nres[AHEAD ? VPT : 1];
-    auto issue = [&](int row, uint4 (&dx)[AHEAD ? VPT : 1], uint4 (&dres)[AHEAD ? VPT : 1]) {
+    uint4 x[VPT], res[VPT], own[OWN ? VPT : 1], nx[AHEAD ? VPT : 1], nres[AHEAD ? VPT : 1], nown[AHEAD && OWN ? VPT : 1];
+    auto issue = [&](int row, uint4 (&dx)[AHEAD ? VPT : 1], uint4 (&dres)[AHEAD ? VPT : 1], uint4 (&down)[AHEAD && OWN ? VPT : 1]) {
         if constexpr (AHEAD) {
             const int len = row < p.rows ? row_len(p, row) : 0;
             const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = grp.tid + i * grp.n;
-                const bool in = FULL ? row < p.rows : v < len;
-                dx[i] = in ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
-                if constexpr (FUSED) dres[i] = in ? ld_stream(reinterpret_cast<const uint4 *>(p.ep.residual) + base + v) : make_uint4(0, 0, 0, 0);
+                const bool inside = FULL ? row < p.rows : v < len;
+                dx[i] = inside ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
+                if constexpr (FUSED) dres[i] = inside ? ld_stream(reinterpret_cast<const uint4 *>(p.ep.residual) + base + v) : make_uint4(0, 0, 0, 0);
+                if constexpr (OWN) down[i] = inside ? ld_stream(in + base + v) : make_uint4(0, 0, 0, 0);
             }
         }
     };
-    if constexpr (AHEAD) issue(vb, nx, nres);
+    if constexpr (AHEAD) issue(vb, nx, nres, nown);
     for (int row = vb; row < p.rows; row += nb) {
         const int len = row_len(p, row);
         const int64_t base = static_cast<int64_t>(row) * p.row_vecs;
@@ -645,13 +679,15 @@ __device__ __forceinline__ void ws_finish(const ArParams &p, int64_t ag_ts, int 
             for (int i = 0; i < VPT; ++i) {
                 x[i] = nx[i];
                 res[i] = nres[i];
+                if constexpr (OWN) own[i] = nown[i];
             }
-            issue(row + nb, nx, nres);
+            issue(row + nb, nx, nres, nown);
         } else {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = grp.tid + i * grp.n;
                 x[i] = (FULL || v < len) ? ld_poll(ag + base + v) : make_uint4(0, 0, 0, 0);
+                if constexpr (OWN) own[i] = (FULL || v < len) ? ld_stream(in + base + v) : make_uint4(0, 0, 0, 0);
             }
             if constexpr (FUSED) load_residual<T, VPT, FULL>(p.ep, seg, row, grp, res);
         }
@@ -659,8 +695,12 @@ __device__ __forceinline__ void ws_finish(const ArParams &p, int64_t ag_ts, int 
         for (int i = 0; i < VPT; ++i) {
             const int v = grp.tid + i * grp.n;
             if (FULL || v < len) {
-                x[i] = wait_landed(ag + base + v, x[i], p.st, p.rank, kStageGather, v / p.vpr);
+                x[i] = wait_landed(ag + base + v, x[i], p.st, p.rank, kStageGather, OWN ? (p.rank ^ 1) : v / p.vpr);
                 st_empty(ag + base + v);
+                if constexpr (OWN) {
+                    const uint4 part[2] = {p.rank == 0 ? own[i] : x[i], p.rank == 0 ? x[i] : own[i]};
+                    x[i] = sum_in_rank_order<T, 2>(part);
+                }
             }
         }
         if constexpr (FUSED) {
@@ -721,6 +761,52 @@ __global__ void __launch_bounds__(kWsMaxThreads, 1)
         reinterpret_cast<uint32_t *>(&p)[i] = reinterpret_cast<const uint32_t *>(params_by_rank + rank)[i];
     __syncthreads();
     ar_ws_body<T, NR, VPT, FUSED>(p, blockIdx.x % nb, nb, sm);
+}
+
+// Two ranks, one hop (see ws_push_rows): finishing warps that add their own row, and pushing warps.  A kernel of
+// its own because it has no reducing warps: 640 threads leave the finishing warps 96 registers for the extra row.
+constexpr int kWs1PushThreads = 128;
+constexpr int kWs1MaxThreads = 512 + kWs1PushThreads;
+
+template <typename T, int VPT>
+__device__ __forceinline__ void ar_ws1_body(const ArParams &p, int vb, int nb, EpilogueSmem &sm) {
+    if (cluster_size() != p.cluster) {   // this kernel is planned without clusters
+        if (threadIdx.x == 0) record_status(p.st, kStatusClusterMismatch, p.rank, vb, kStageGather, p.rank, cluster_size());
+        return;
+    }
+    begin_call(p.st, nb, sm);
+    if (threadIdx.x == 0) sm.rows_finished = 0;
+    __syncthreads();
+    const int64_t ag_ts = static_cast<int64_t>(sm.seq & 1ull) * p.ag_stride;
+    const int tid = threadIdx.x;
+    if (tid < p.tf) {
+        const Group grp{tid, p.tf, 1};
+        if (p.full) ws_finish<T, VPT, true, true, true>(p, ag_ts, vb, nb, grp, sm);
+        else ws_finish<T, VPT, true, false, true>(p, ag_ts, vb, nb, grp, sm);
+    } else {
+        ws_push_rows<T>(p, ag_ts, vb, nb, tid - p.tf, p.ts, &sm.rows_finished);
+    }
+}
+
+template <typename T, int VPT>
+__global__ void __launch_bounds__(kWs1MaxThreads, 1)
+    ar_ws1_kernel(const __grid_constant__ ArParams p) {
+    __shared__ EpilogueSmem sm;
+    grid_dependency_sync();
+    ar_ws1_body<T, VPT>(p, blockIdx.x, gridDim.x, sm);
+}
+
+// The two ranks in one launch on one GPU (see ar_emulated_kernel).
+template <typename T, int VPT>
+__global__ void __launch_bounds__(kWs1MaxThreads, 1)
+    ar_ws1_emulated_kernel(const ArParams *params_by_rank, int nb) {
+    __shared__ EpilogueSmem sm;
+    __shared__ ArParams p;
+    const int rank = blockIdx.x / nb;
+    for (int i = threadIdx.x; i < static_cast<int>(sizeof(ArParams) / 4); i += blockDim.x)
+        reinterpret_cast<uint32_t *>(&p)[i] = reinterpret_cast<const uint32_t *>(params_by_rank + rank)[i];
+    __syncthreads();
+    ar_ws1_body<T, VPT>(p, blockIdx.x % nb, nb, sm);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -15,7 +15,8 @@ struct ArShape {
     int threads;
     int grid;        // CTAs per rank (a multiple of `cluster`)
     int cluster;     // CTAs per thread-block cluster (1: launched without a cluster attribute)
-    int ws;          // 1: the warp-specialised two-shot kernel (vpt: vectors per finishing thread, threads: all roles)
+    int ws;          // 1: the warp-specialised two-shot kernel (vpt: vectors per finishing thread, threads: all roles);
+                     // 2: its two-rank one-hop variant (finishing and pushing warps only)
     int sym;         // 0: push exchange; 1: exchange through symmetric memory with peer loads;
                      // 2: the same with NVSwitch multicast (two_shot is true for 1 and 2)
 };

@@ -33,6 +33,13 @@ static const void *ar_ws_fn(bool emulated) {
 template <typename T, int NR, int VPT>
 static const void *ar_fn_modes(const ArShape &s, bool emulated) {
     if (s.sym) return ar_sym_fn<T, NR, VPT>(s, emulated);
+    if (s.ws == 2) {   // two ranks, one hop, fused operator
+        if constexpr (NR == 2) {
+            if (s.fused) return emulated ? reinterpret_cast<const void *>(&ar_ws1_emulated_kernel<T, VPT>)
+                                         : reinterpret_cast<const void *>(&ar_ws1_kernel<T, VPT>);
+        }
+        return nullptr;
+    }
     if (s.ws) {
         if (s.fused) return ar_ws_fn<T, NR, VPT, true>(emulated);
         if constexpr (VPT == 2) return ar_ws_fn<T, NR, VPT, false>(emulated);   // the plain all-reduce views rows of 1024 vectors

@@ -249,6 +249,44 @@ def test_two_shot_with_specialised_warps(world, tokens, hidden, quant, dtype):
                 assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8))
 
 
+@pytest.mark.parametrize("tokens,hidden,quant,dtype", [
+    (300, 8192, 3, torch.bfloat16), (1500, 1024, 1, torch.bfloat16), (301, 7168, 4, torch.bfloat16), (333, 2056, 0, torch.bfloat16),
+    (160, 16384, 3, torch.bfloat16), (200, 4096, 2, torch.float16), (180, 1000, 3, torch.float32)])
+def test_two_ranks_one_hop_and_two_hops_agree(tokens, hidden, quant, dtype):
+    """At two ranks the kernel with specialised warps sends whole rows to the peer and every rank adds its own row
+    while finishing (one hop); the option two_rank_one_hop = 0 keeps reduce-scatter + all-gather (two hops).  Both
+    must give the oracle's result and each other's bits, call after call on one workspace, in either order."""
+    static = 0.05 if quant == 4 else None
+    with util.EmulatedGroup(2, max_bytes=16 << 20) as g:
+        for call, one_hop in enumerate([1, 0, 0, 1, 1]):
+            g.set_option("two_rank_one_hop", one_hop)
+            parts, res, w = util.random_case(2, tokens, hidden, dtype, seed=tokens + call // 2)
+            outs = g.fused([p.cuda() for p in parts], res.cuda(), w.cuda(), 1e-6, quant, static, force_mode=TWO_SHOT)
+            want = eo.epilogue_t1(parts, res, w, 1e-6, quant, static)
+            for got in outs:
+                util.check_against_oracle(got, want, quant, exact_residual=dtype != torch.float32)
+                assert torch.equal(got[1].view(torch.uint8), outs[0][1].view(torch.uint8))
+            if call % 2 == 1:      # same inputs as the call before, the other exchange
+                for a, b in zip(outs, prev):
+                    assert torch.equal(a[0].view(torch.uint8), b[0].view(torch.uint8))
+                    assert torch.equal(a[1].view(torch.uint8), b[1].view(torch.uint8))
+            prev = outs
+
+
+def test_two_ranks_output_over_the_input_takes_two_hops():
+    """residual_out may be the input buffer itself.  The one-hop exchange reads the input while it finishes rows, so
+    the call must notice the overlap and take the two-hop exchange, which never reads a row after finishing it."""
+    tokens, hidden = 400, 4096
+    parts, res, w = util.random_case(2, tokens, hidden, torch.bfloat16, seed=21)
+    want = eo.epilogue_t1(parts, res, w, 1e-6, 3)
+    with util.EmulatedGroup(2, max_bytes=8 << 20) as g:
+        d_parts = [p.cuda() for p in parts]
+        outs = [util.alloc_outputs(p, 3) for p in d_parts]
+        outs = [(d_parts[r], o[1], o[2]) for r, o in enumerate(outs)]      # residual_out over the input
+        got = g.fused(d_parts, res.cuda(), w.cuda(), 1e-6, 3, force_mode=TWO_SHOT, outs=outs)
+    _check_all_ranks(got, want, 3)
+
+
 def _emulated_call_async(g, parts, res, w, quant, outs):
     import ctypes
     from gpuk_b200 import cabi
