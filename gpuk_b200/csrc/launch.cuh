@@ -23,7 +23,7 @@ struct ArShape {
 
 // Launches `fn` (one parameter block behind args) with an optional cluster dimension; with
 // `all_resident` the launch is cooperative, i.e. refused unless the whole grid fits the GPU.
-// Other launches are programmatic dependent launches (unless GPUK_PDL=0): the kernels wait
+// Other launches are programmatic dependent launches : the kernels wait
 // for the preceding grid themselves (griddepcontrol.wait) before they touch memory, so their
 // CTAs may be placed on the SMs while the tail of the preceding kernel is still running.
 cudaError_t launch_kernel(const void *fn, int grid, int threads, int cluster, bool all_resident, void **args, cudaStream_t stream,
