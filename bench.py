@@ -909,6 +909,79 @@ def run_crossover(env, gpuk, rank, world, barrier, hidden=8192):
 # ---------------------------------------------------------------------------------------
 # a short, fixed case of one kernel: the command to put under ncu
 # ---------------------------------------------------------------------------------------
+def run_fp8_linear(tokens=32, iters=200, k_split=0):
+    """The linear layer behind the fused operator at decode batch sizes, per rank of the eight-way decoder of config 5
+    (q|k|v, w1|w3, vocabulary shard): this library's weight-streaming FP8 kernel, torch._scaled_mm on the same FP8
+    operands, and the bf16 F.linear a caller without the FP8 hand-off would run.  Microseconds per call from CUDA
+    events; the weights of a shape rotate over enough copies to exceed L2, so every call streams them from HBM."""
+    import gpuk_b200 as gpuk
+    dev = torch.device("cuda", torch.cuda.current_device())
+    peak = measured_hbm_peak()[0]
+    rows = []
+    for name, n, k in (("wq|wk|wv", 1280, 8192), ("w1|w3", 7168, 8192), ("vocabulary shard", 4096, 8192)):
+        copies = max(2, int(math.ceil(3 * L2_BYTES / (n * k))))
+        g = torch.Generator(device=dev).manual_seed(n + k)
+        wq = [torch.randn(n, k, generator=g, device=dev).mul_(100).clamp_(-448, 448).to(torch.float8_e4m3fn) for _ in range(copies)]
+        wb = [w.to(torch.bfloat16) for w in wq[:max(2, copies // 2)]]
+        x = torch.randn(tokens, k, generator=g, device=dev).mul_(100).clamp_(-448, 448).to(torch.float8_e4m3fn)
+        xb = x.to(torch.bfloat16)
+        xs = torch.rand(tokens, 1, generator=g, device=dev) * 0.02 + 1e-3
+        wsc = torch.rand(1, n, generator=g, device=dev) * 0.02 + 1e-3
+        out = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
+
+        def timed(fn, ncopies):
+            """Device time per call: `iters` calls captured into one CUDA graph (no host launch cost between them)."""
+            for i in range(3):
+                fn(i % ncopies)
+            torch.cuda.synchronize()
+            if iters < 20:      # a short run (to put under a profiler): plain launches
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(iters):
+                    fn(i % ncopies)
+                e1.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1) * 1e3 / iters
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(iters):
+                        fn(i % ncopies)
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / iters
+
+        own = timed(lambda i: gpuk.fp8_linear(x, xs, wq[i], wsc, out, k_split=k_split), copies)
+        wp = [gpuk.fp8_pack_weight(w) for w in wq]
+        own_packed = timed(lambda i: gpuk.fp8_linear(x, xs, wp[i], wsc, out, packed=True, k_split=k_split), copies)
+        del wp
+        got = out.clone()
+        lib = timed(lambda i: torch._scaled_mm(x, wq[i].t(), scale_a=xs, scale_b=wsc, out_dtype=torch.bfloat16), copies)
+        want = torch._scaled_mm(x, wq[(iters - 1) % copies].t(), scale_a=xs, scale_b=wsc, out_dtype=torch.bfloat16)
+        bf16 = timed(lambda i: F_linear(xb, wb[i]), len(wb))
+        steps_apart = (got.view(torch.int16).int() - want.view(torch.int16).int()).abs().max().item()
+        nbytes = n * k + tokens * k + tokens * n * 2
+        rows.append({"layer": name, "tokens": tokens, "n": n, "k": k, "weight_bytes": n * k,
+                     "gpuk_b200_us": own_packed, "gpuk_b200_row_major_weights_us": own, "torch_scaled_mm_us": lib, "bf16_linear_us": bf16,
+                     "gpuk_b200_gbs": nbytes / own_packed * 1e-3, "frac_of_hbm_peak": nbytes / own_packed * 1e-3 / peak,
+                     "torch_scaled_mm_frac_of_hbm_peak": nbytes / lib * 1e-3 / peak,
+                     "max_bf16_steps_from_scaled_mm": steps_apart})
+    cabi_status = gpuk.cabi.lib.gpuk_fp8_linear_status()
+    return {"case": "fp8_linear", "kernel": "fp8_linear_skinny_kernel (mma.sync e4m3, weights streamed once)", "status": cabi_status,
+            "hbm_peak_gbs": peak, "rows": rows}
+
+
+def F_linear(x, w):
+    return torch.nn.functional.linear(x, w)
+
+
 def run_case(a):
     """`--case norm_quant`: the one-GPU kernel `--iters` times; `--case emulated`: the N-rank exchange for all
     ranks inside one launch on this GPU (--mode 1 = one-shot, 2 = two-shot).  Seeded random bf16 inputs; nothing
@@ -935,6 +1008,10 @@ def run_case(a):
                                                         a.hidden, cabi.DTYPE_BF16, 1e-6, a.quant, stream))
         torch.cuda.synchronize()
         print("norm_quant", a.tokens, a.hidden, "scale0", float(scale[0]))
+        return
+    if a.case == "fp8_linear":
+        for tokens in ([a.tokens] if a.tokens <= 32 else [8, 16, 32]):
+            print(json.dumps(run_fp8_linear(tokens, a.iters)), flush=True)
         return
     n = a.world
     msg = a.tokens * a.hidden * 2
@@ -988,7 +1065,7 @@ def main():
                     help="also time the producer GEMM + the exchange of the prefill shape, serial and overlapped through ready words")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="workspace tuning option for the exchange (gpuk_ws_set_option), e.g. two_shot_ws=0; repeatable")
-    ap.add_argument("--case", choices=["norm_quant", "emulated"], help="run one short fixed case of a kernel and exit")
+    ap.add_argument("--case", choices=["norm_quant", "emulated", "fp8_linear"], help="run one short fixed case of a kernel and exit")
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--quant", type=int, default=3)

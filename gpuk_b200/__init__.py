@@ -76,6 +76,58 @@ if os.environ.get("GPUK_FP8_POLICY"):
     set_fp8_policy(os.environ["GPUK_FP8_POLICY"])
 
 
+def fp8_linear_supported(tokens: int, out_features: int, in_features: int) -> bool:
+    """Shapes ``fp8_linear`` is built for: decode batches (at most 32 tokens), 128-channel tiles, 64-byte k steps."""
+    return 0 < tokens <= 32 and out_features % 128 == 0 and in_features % 64 == 0
+
+
+def fp8_pack_weight(w_fp8: torch.Tensor) -> torch.Tensor:
+    """FP8 weights [n, k] rearranged once into the blocked layout ``fp8_linear(..., packed=True)`` reads fastest
+    (16 rows x 64 bytes per contiguous KiB); n a multiple of 16, k of 64.  Returns a new [n, k]-shaped tensor whose
+    bytes are in blocked order."""
+    import ctypes
+    if w_fp8.dtype != torch.float8_e4m3fn or not (w_fp8.is_cuda and w_fp8.is_contiguous() and w_fp8.dim() == 2):
+        raise RuntimeError("gpuk: fp8_pack_weight takes a contiguous 2-d float8_e4m3fn CUDA tensor")
+    packed = torch.empty_like(w_fp8)
+    with torch.cuda.device(w_fp8.device):
+        cabi.check(cabi.lib.gpuk_fp8_pack_weight(ctypes.c_void_p(w_fp8.data_ptr()), ctypes.c_void_p(packed.data_ptr()),
+                                                 w_fp8.shape[0], w_fp8.shape[1],
+                                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return packed
+
+
+def fp8_linear(x_fp8: torch.Tensor, x_scale: torch.Tensor, w_fp8: torch.Tensor, w_scale: torch.Tensor,
+               out: Optional[torch.Tensor] = None, *, packed: bool = False, k_split: int = 0) -> torch.Tensor:
+    """``(x_fp8 @ w_fp8.T) * x_scale[:, None] * w_scale[None, :]`` in bf16 for at most 32 tokens: the linear layer
+    that consumes ``norm_out`` / ``scale_out`` of the fused operator (``F.linear`` in ``model/tensor_parallel.py:66``;
+    the reference has no FP8 path).  ``x_fp8`` [tokens, k] and ``w_fp8`` [n, k] are ``float8_e4m3fn``, ``x_scale``
+    holds one fp32 scale per token (any shape with ``tokens`` elements), ``w_scale`` one per output channel;
+    ``packed=True`` says ``w_fp8`` came from ``fp8_pack_weight``.
+    Hand-written weight-streaming kernel (``csrc/fp8_linear.cu``); raises for shapes it is not built for --
+    ``fp8_linear_supported`` tells, and larger batches belong to a library GEMM."""
+    import ctypes
+    if x_fp8.dtype != torch.float8_e4m3fn or w_fp8.dtype != torch.float8_e4m3fn:
+        raise RuntimeError("gpuk: fp8_linear takes float8_e4m3fn operands")
+    if not (x_fp8.is_cuda and x_fp8.is_contiguous() and w_fp8.is_contiguous() and x_fp8.dim() == 2 and w_fp8.dim() == 2):
+        raise RuntimeError("gpuk: fp8_linear takes contiguous 2-d CUDA tensors")
+    m, k = x_fp8.shape
+    n = w_fp8.shape[0]
+    if w_fp8.shape[1] != k or x_scale.numel() != m or w_scale.numel() != n:
+        raise RuntimeError("gpuk: fp8_linear operand shapes do not match")
+    if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32 or not x_scale.is_contiguous() or not w_scale.is_contiguous():
+        raise RuntimeError("gpuk: fp8_linear takes contiguous fp32 scales")
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=x_fp8.device)
+    elif out.dtype != torch.bfloat16 or out.shape != (m, n) or not out.is_contiguous():
+        raise RuntimeError("gpuk: fp8_linear writes a contiguous bf16 [tokens, n] tensor")
+    with torch.cuda.device(x_fp8.device):
+        cabi.check(cabi.lib.gpuk_fp8_linear_skinny(
+            ctypes.c_void_p(x_fp8.data_ptr()), ctypes.c_void_p(x_scale.data_ptr()), ctypes.c_void_p(w_fp8.data_ptr()),
+            ctypes.c_void_p(w_scale.data_ptr()), ctypes.c_void_p(out.data_ptr()), m, n, k, 1 if packed else 0, k_split,
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return out
+
+
 class _TorchOps:
     """The operator set GPUKDistEnv drives; tests substitute a recording fake."""
     init_ar_fusion = staticmethod(init_ar_fusion)

@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
 ]
-CORE_SOURCES = ["core.cu", "launch_bf16.cu", "launch_f16.cu", "launch_f32.cu", "noalloc.cu"]
+CORE_SOURCES = ["core.cu", "launch_bf16.cu", "launch_f16.cu", "launch_f32.cu", "noalloc.cu", "fp8_linear.cu"]
 HEADERS = ["common.cuh", "epilogue.cuh", "kernels.cuh", "launch.cuh", "launch_impl.cuh",
            os.path.join(ROOT, "include", "gpuk_b200.h")]
 

@@ -77,6 +77,9 @@ _SIGNATURES = {
     "gpuk_selfcheck_allreduce_rms": (c_int, [c_int, POINTER(_P), _P, _P, POINTER(_P), POINTER(_P), POINTER(_P),
                                              c_int64, c_int, c_int, c_float, c_int, c_int, _P]),
     "gpuk_selfcheck_status": (c_int, [POINTER(c_uint32), _P]),
+    "gpuk_fp8_linear_skinny": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
+    "gpuk_fp8_pack_weight": (c_int, [_P, _P, c_int, c_int, _P]),
+    "gpuk_fp8_linear_status": (c_int, []),
 }
 for _name, (_res, _args) in _SIGNATURES.items():
     _fn = getattr(lib, _name)

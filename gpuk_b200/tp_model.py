@@ -12,7 +12,10 @@ replaces ``reduce_from_tensor_parallel_region`` + ``x + ...`` + the following ``
 (``tensor_parallel.py:117-118``, ``transformer_model.py:610-618``) at both sites of every
 layer.  With ``fp8=True`` the normalised activations leave the operator as FP8-e4m3 with one
 scale per token, and the column-parallel projections that consume them run as FP8 GEMMs with
-row-wise scales (``torch._scaled_mm``; a library GEMM, outside the hand-written path).
+row-wise scales: ``torch._scaled_mm`` (a library GEMM) by default, or -- ``own_fp8_gemm=True``, decode batches of
+at most 32 tokens -- this library's own weight-streaming kernel (``gpuk_b200.fp8_linear``, ``csrc/fp8_linear.cu``),
+which gives the same results to within one bf16 step and is slower than the library on B200 at the
+benchmark's shapes (measured in ``bench.py --case fp8_linear``).
 
 ``fused=False`` runs the reference arrangement on the same weights -- NCCL ``all_reduce``, then
 add, RMSNorm (and quantisation) as separate PyTorch operators -- and is the comparison arm.
@@ -69,9 +72,11 @@ def _xavier(out_f: int, in_f: int, gen: torch.Generator, device, dtype) -> torch
 class _Linear:
     """y = x @ W^T for one shard, in the activation dtype or as an FP8 GEMM with row-wise scales."""
 
-    def __init__(self, weight: torch.Tensor, fp8: bool):
+    def __init__(self, weight: torch.Tensor, fp8: bool, own_gemm: bool = False):
         self.weight = weight                                  # [out_local, in]
         self.fp8 = fp8
+        self.own_gemm = own_gemm                              # decode batches: this library's weight-streaming FP8 kernel
+        self.w_packed = None                                  # ... its blocked copy of the weights, made at first use
         if fp8:
             amax = weight.float().abs().amax(dim=1, keepdim=True).clamp_(min=1e-12)
             self.w_scale = (amax / 448.0).t().contiguous()    # [1, out_local] fp32, one scale per output channel
@@ -79,6 +84,12 @@ class _Linear:
 
     def __call__(self, x: torch.Tensor, x_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.fp8 and x.dtype == torch.float8_e4m3fn:
+            if self.own_gemm and x.is_cuda:
+                import gpuk_b200 as gpuk
+                if gpuk.fp8_linear_supported(x.shape[0], self.w_q.shape[0], self.w_q.shape[1]) and self.weight.dtype == torch.bfloat16:
+                    if self.w_packed is None:
+                        self.w_packed = gpuk.fp8_pack_weight(self.w_q)
+                    return gpuk.fp8_linear(x, x_scale, self.w_packed, self.w_scale, packed=True)
             return torch._scaled_mm(x, self.w_q.t(), scale_a=x_scale, scale_b=self.w_scale, out_dtype=self.weight.dtype)
         return F.linear(x, self.weight)
 
@@ -87,7 +98,7 @@ class TPDecoder:
     """Random-initialised decoder, sharded over the ranks of ``env``'s group; inference only."""
 
     def __init__(self, args: DecoderArgs, env, *, device, fused: bool = True, fp8: bool = True, seed: int = 1234,
-                 master_init: bool = False, max_batch: int = 32):
+                 master_init: bool = False, max_batch: int = 32, own_fp8_gemm: bool = False):
         self.args, self.env, self.device, self.fused, self.fp8 = args, env, torch.device(device), fused, fp8
         self.rank, self.world = env.rank, env.world_size
         a, w, r = args, self.world, self.rank
@@ -120,9 +131,9 @@ class TPDecoder:
             norm_gen = torch.Generator(device="cpu").manual_seed(seed * 1000 + t + 8)
             self.layers.append({
                 # one GEMM for q|k|v and one for w1|w3: they share their input
-                "wqkv": _Linear(torch.cat([wq, wk, wv], 0), fp8),
+                "wqkv": _Linear(torch.cat([wq, wk, wv], 0), fp8, own_fp8_gemm),
                 "wo": _Linear(make(a.dim, a.n_heads * hd, t + 4, "cols"), False),
-                "w13": _Linear(torch.cat([w1, w3], 0), fp8),
+                "w13": _Linear(torch.cat([w1, w3], 0), fp8, own_fp8_gemm),
                 "w2": _Linear(make(a.dim, a.ffn_dim, t + 7, "cols"), False),
                 "attention_norm": (1 + 0.1 * torch.randn(a.dim, generator=norm_gen)).to(a.dtype).to(self.device),
                 "ffn_norm": (1 + 0.1 * torch.randn(a.dim, generator=norm_gen)).to(a.dtype).to(self.device),
@@ -131,7 +142,7 @@ class TPDecoder:
             })
         norm_gen = torch.Generator(device="cpu").manual_seed(seed * 1000 + 9)
         self.norm = (1 + 0.1 * torch.randn(a.dim, generator=norm_gen)).to(a.dtype).to(self.device)
-        self.output = _Linear(make(a.vocab_size, a.dim, 2, "rows"), fp8)
+        self.output = _Linear(make(a.vocab_size, a.dim, 2, "rows"), fp8, own_fp8_gemm)
         inv = 1.0 / (a.rope_theta ** (torch.arange(0, hd, 2, dtype=torch.int64).float() / hd))   # :497-502
         freqs = torch.outer(torch.arange(a.max_seq_len * 2, dtype=torch.float32), inv)
         self.cos, self.sin = freqs.cos().to(self.device), freqs.sin().to(self.device)

@@ -323,6 +323,36 @@ int gpuk_emulated_allreduce_rms(gpuk_ws *const *ws, int world_size, void *const 
                                 int dtype, float eps, int quant_type, int force_mode, void *stream);
 
 /*
+ * The consumer of the fused operator's FP8 output for decode batches: out[m, n] (bf16) =
+ * (x . w^T)[m, n] * x_scale[m] * w_scale[n], with x [m, k] and w [n, k] e4m3 (k contiguous), fp32
+ * accumulation, one rounding.  x and x_scale are norm_out and scale_out of gpuk_allreduce_rms
+ * (quant_type 3 or 1) as they are; w_scale holds one scale per output channel.  Replaces the F.linear that
+ * follows the norm in model/tensor_parallel.py:66 (the reference has no FP8 path; a PyTorch caller would
+ * otherwise use torch._scaled_mm).  Built for the weight-streaming regime: m <= 32 tokens
+ * (GPUK_ERR_UNSUPPORTED beyond -- use a library GEMM there), n a multiple of 128, k a multiple of 64,
+ * operands 16-byte aligned.  w_layout: 0 = w is [n, k] row-major as PyTorch holds it; 1 = w was rearranged once by
+ * gpuk_fp8_pack_weight, so that the 16 rows x 64 bytes a warp multiplies at a time are one contiguous KiB and a
+ * warp reads its rows as one sequential run of memory (rows that lie a power of two apart do not).  k_split = CTAs
+ * of a thread-block cluster that share a tile of 128 output channels and split k (1, 2, 4, 8; 0: chosen from the
+ * shape).  The sum order is fixed, so results are reproducible from call to call.
+ */
+int gpuk_fp8_linear_skinny(const void *x_fp8, const float *x_scale, const void *w_fp8, const float *w_scale,
+                           void *out_bf16, int m, int n, int k, int w_layout, int k_split, void *stream);
+/*
+ * Rearranges FP8 weights [n, k] (row-major) into the blocked layout of w_layout = 1: block (n / 16, k / 64) holds
+ * 16 rows x 64 bytes, row r at byte r * 64; the blocks of a 16-row band follow each other along k.  Done once per
+ * weight matrix (the reference keeps its weights as nn.Linear does, model/tensor_parallel.py:62-67).  n a multiple
+ * of 16, k of 64; `packed` holds n * k bytes and must not overlap w_fp8.
+ */
+int gpuk_fp8_pack_weight(const void *w_fp8, void *packed, int n, int k, void *stream);
+/*
+ * Synchronises the current device and returns GPUK_ERR_BAD_LAUNCH if a gpuk_fp8_linear_skinny launch on it
+ * found itself in another thread-block cluster than planned (it then wrote nothing), else GPUK_OK.
+ * Same contract as status 3 of gpuk_ws_status; the reference has no counterpart (impl.h launches no clusters).
+ */
+int gpuk_fp8_linear_status(void);
+
+/*
  * No counterpart in the reference.  Same job as gpuk_emulated_allreduce_rms (fused op only)
  * for callers that must not allocate device memory -- a health probe or test harness inside a
  * process whose own arena already owns the GPU's memory, where a library-side cudaMalloc may

@@ -227,3 +227,28 @@ def test_fused_decoder_on_one_gpu():
         err = (logits[0] - logits[1]).abs().max().item()
         ref = logits[1].abs().max().item()
         assert err <= (0.08 if fp8 else 0.03) * max(ref, 1e-3), (fp8, err, ref)
+
+
+@pytest.mark.gpu
+def test_decoder_with_this_librarys_fp8_linear_matches_the_library_gemm_on_one_gpu():
+    """own_fp8_gemm=True routes q|k|v, w1|w3 and the vocabulary projection of a decode step through
+    gpuk_fp8_linear_skinny (blocked weights); both GEMMs round fp32-accurate sums once, so the logits agree closely."""
+    import torch.distributed as dist
+    import gpuk_b200
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(_free_port()))
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    env = gpuk_b200.GPUKDistEnv(group=None, device_id=0)
+    args = DecoderArgs(**MID)
+    tokens = torch.randint(0, args.vocab_size, (4, 1), generator=torch.Generator().manual_seed(3)).cuda()
+    logits = []
+    for own in (True, False):
+        m = TPDecoder(args, env, device="cuda:0", fused=True, fp8=True, max_batch=4, own_fp8_gemm=own)
+        m.fill_kv_cache(128)
+        logits.append(m.forward(tokens, torch.tensor([128], device="cuda:0"), cache_len=129).float())
+        if own:
+            assert m.layers[0]["wqkv"].w_packed is not None      # the kernel was taken, not the library fallback
+    err = (logits[0] - logits[1]).abs().max().item()
+    ref = logits[1].abs().max().item()
+    assert err <= 0.02 * max(ref, 1e-3), (err, ref)
