@@ -1183,7 +1183,8 @@ def main():
                     "frac_of_measured_peer_copy_770": ach / NVLINK_PEER_COPY_GBS,
                     "frac_of_measured_sm_store_690": ach / NVLINK_SM_STORE_GBS,
                     "algorithmic_bytes_per_launch": bus_bytes(cfg.tokens, cfg.hidden, world),
-                    "kernel": "ar_kernel (two-shot, fused epilogue)"}
+                    "kernel": ("ar_ws1_kernel (two ranks: whole rows in one hop, specialised warps, fused epilogue)" if world == 2 else
+                               "ar_ws_kernel (two-shot, specialised warps, fused epilogue)")}
         line = {
             "metric": METRIC, "value": us, "unit": "us/call", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": us * 1e-3, "higher_is_better": False,

@@ -877,12 +877,15 @@ int build_ar_call(gpuk_ws *ws, const CallArgs &a, int force_mode, bool emulated,
         // rank's input themselves, so the outputs must not overlap it (a finished row would overwrite input that has
         // not been pushed yet), and an input still in the making (ready words) keeps the two-hop exchange, whose
         // finishing warps never touch the input.
-        auto overlaps_in = [&](const void *q, int64_t bytes) {
-            const char *b = static_cast<const char *>(q), *i0 = static_cast<const char *>(a.in);
-            return q && b < i0 + plan.message_bytes && i0 < b + bytes;
+        auto overlaps_in = [&](const void *o, int64_t bytes) {
+            const char *b = static_cast<const char *>(o), *i0 = static_cast<const char *>(a.in);
+            return o && b < i0 + plan.message_bytes && i0 < b + bytes;
         };
+        // exact sizes: two live tensors that merely lie next to each other must not count, or ranks whose allocators
+        // placed them differently would pick different kernels (aliasing on purpose is the same on every rank)
+        const int64_t norm_bytes = q.mode == kQuantNone ? plan.message_bytes : a.numel;
         p->one_hop = (ws->world == 2 && fused && ws->opt_two_rank_one_hop && !ws->ready &&
-                      !overlaps_in(a.residual_out, plan.message_bytes) && !overlaps_in(a.norm_out, plan.message_bytes)) ? 1 : 0;
+                      !overlaps_in(a.residual_out, plan.message_bytes) && !overlaps_in(a.norm_out, norm_bytes)) ? 1 : 0;
         if (p->one_hop) p->ts = kWs1PushThreads, p->tr = 0;
     }
     p->lead_push = std::max(1, ws->opt_lead_push > 0 ? ws->opt_lead_push : plan.lead_push);

@@ -261,7 +261,8 @@ int gpuk_ws_set_oneshot_max_bytes(gpuk_ws *ws, int64_t bytes);
  * kernel with specialised warps, 0: the lock-step kernel), "two_rank_one_hop" (1, the default: at two ranks that
  * kernel pushes whole rows into the peer's staging and every rank adds its own row while finishing, one NVLink hop
  * for the bytes the two hops of reduce-scatter + all-gather would move; 0: two hops.  The fused call falls back to
- * two hops by itself when ready words are set or an output overlaps the input), "ws_finish_threads" / "ws_reduce_threads" /
+ * two hops by itself when ready words are set or an output overlaps the input -- which, like everything about a
+ * call, must be the same on every rank), "ws_finish_threads" / "ws_reduce_threads" /
  * "ws_scatter_threads" (its threads per role, 0: default), "ws_scatter_lead" (rows its scatter may run ahead of
  * its finish, -1: default, 0: unbounded), "ws_max_ctas" (SMs it may occupy, 0: all), "gather_multicast" (1: its
  * gather goes through the multicast address of the attached symmetric memory), "lead_push" / "lead_reduce" (pipeline

