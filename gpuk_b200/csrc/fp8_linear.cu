@@ -8,7 +8,7 @@
 //
 //   * weights [n, k] (k contiguous, e4m3) are the 16-row operand of the warp-level mma and the
 //     activations [tokens, k] its 8-column operand, so one weight fragment is used for all four
-//     groups of 8 tokens; the weights go from global memory straight into the fragment registers.
+//     groups of 8 tokens; every thread fetches exactly the bytes of its own fragment registers.
 //     sm_100 has no native FP8 path for mma.sync (ptxas expands an e4m3 mma into conversions and
 //     f16 HMMAs per instruction, 170 instructions per 64-byte k step as first written), so the
 //     kernel converts e4m3 -> f16 itself (exact), once per weight fragment instead of once per
@@ -22,9 +22,9 @@
 //     bytes of 8 rows: whole 32-byte sectors, nothing wasted.
 //   * a tile of 128 output channels is shared by a thread-block cluster of KS CTAs that split k;
 //     inside a CTA the eight warps split the channels (16 each, one fragment), so a CTA needs no
-//     reduction of its own.  The activations of the CTA's k-range are staged through shared memory once (cp.async)
-//     and read by all four warps.  The KS partial tiles are summed through distributed shared
-//     memory in a fixed order (deterministic, no atomics), scaled, rounded once and stored.
+//     reduction of its own.  Weights and activations arrive by cp.async (the pipeline is described at
+//     the kernel).  The KS partial tiles are summed through distributed shared memory in a fixed
+//     order (deterministic, no atomics), scaled, rounded once and stored.
 //
 // Activation traffic is (n / 128) x tokens x k bytes out of L2 against n x k bytes of weights from
 // HBM: a quarter of it at 32 tokens.
@@ -41,12 +41,18 @@ namespace {
 
 constexpr int kTileN = 128;        // output channels per cluster
 constexpr int kWarps = 8;          // per CTA; each owns kTileN / kWarps = 16 channels = one 16-row fragment
-constexpr int kRing = 8;           // k steps of weights a thread keeps in flight: 16 x 16 bytes
+constexpr int kThreads = kWarps * 32;
+constexpr int kDepth = 8;          // k steps of weights in flight per thread (cp.async groups): 7 x 32 bytes
 constexpr int kTokens = 32;        // token capacity of one pass: four groups of 8
 constexpr int kStepBytes = 64;     // k bytes one warp-wide 16-byte load covers per row
-constexpr int kChunkSteps = 16;    // k steps staged per round: 1 KiB of every token's row
-constexpr int kXRow = kChunkSteps * kStepBytes + 64;   // shared-memory row pitch; 64 mod 128 keeps 16-byte reads conflict-free
-constexpr int kPartPitch = 36;     // floats per channel row of the partial tile (32 tokens + padding)
+constexpr int kXSteps = 8;         // k steps of activations staged together (two such buffers)
+constexpr int kXRow = kXSteps * kStepBytes + 64;   // shared-memory row pitch; 64 mod 128 keeps 16-byte reads conflict-free
+constexpr int kXBuf = kTokens * kXRow;              // one activation buffer
+constexpr int kWSlot = 2 * kThreads * 16;           // one k step of the CTA's weights: two 16-byte vectors per thread
+constexpr int kPartPitch = kTileN + 4;              // floats per token row of the partial tile (128 channels + padding)
+constexpr int kSmemBytes = kDepth * kWSlot + 2 * kXBuf;   // 64 KiB + 36 KiB: two CTAs per SM
+static_assert(kTokens * kPartPitch * 4 <= kDepth * kWSlot, "the partial tile reuses the weight ring");
+static_assert((kDepth & (kDepth - 1)) == 0 && kXSteps == kDepth, "slot and buffer arithmetic below");
 
 struct Fp8LinearParams {
     const uint8_t *x;        // [m, k] e4m3
@@ -59,13 +65,6 @@ struct Fp8LinearParams {
     int packed;              // weight layout: 0 = [n, k] row-major, 1 = blocked (gpuk_fp8_pack_weight)
     int *status;             // set to 1 when the launch did not carry the planned cluster (nothing is written then)
 };
-
-__device__ __forceinline__ uint4 ld_weights(const uint8_t *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem, bool valid) {
     const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -101,11 +100,23 @@ __device__ __forceinline__ float ld_cluster_f32(const float *local, int cta) {
     return v;
 }
 
-__global__ void __launch_bounds__(kWarps * 32, 2) fp8_linear_skinny_kernel(const __grid_constant__ Fp8LinearParams p) {
-    // activations of one round (32 tokens x 1 KiB); afterwards the CTA's partial tile (128 x 32 fp32) lives in the same memory
-    __shared__ __align__(16) unsigned char smem[kTokens * kXRow];
-    static_assert(kTileN * kPartPitch * 4 <= kTokens * kXRow, "the partial tile reuses the activation stage");
-    static_assert(kChunkSteps % kRing == 0, "a round of activations is a whole number of ring turns");
+// QN = groups of 8 tokens in use (1 .. 4): the token loop has no run-time bounds.
+//
+// Pipeline of one thread.  Weights: step j of the CTA's k range is fetched with two 16-byte cp.async into the
+// thread's own place in slot j % kDepth of a shared-memory ring (it will read them back itself, so no barrier is
+// involved) and committed as group j; before step i is multiplied, step i + kDepth - 1 is issued and
+// cp.async.wait_group leaves at most kDepth - 1 groups pending, i.e. group i is complete.  Asynchronous copies are
+// tracked by group, not by register scoreboards, so all seven steps ahead really are in flight (a ring of registers
+// filled by plain loads is not: a warp has a handful of scoreboards, and waiting for the oldest load waits for
+// younger ones on the same scoreboard too).  Activations: whenever the issue front enters a new chunk of kXSteps
+// steps, all threads together fetch that chunk (every token's 512 bytes) into the activation buffer the chunk
+// before last used, inside the same group; when the multiply front enters the chunk, every thread has waited for
+// its own copies and one block barrier makes the chunk visible to all warps.
+template <int QN>
+__global__ void __launch_bounds__(kThreads, 2) fp8_linear_skinny_kernel(const __grid_constant__ Fp8LinearParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char *wring = smem;                          // [kDepth][2][kThreads] x 16 bytes
+    unsigned char *xbuf = smem + kDepth * kWSlot;         // [2][kTokens][kXRow]
     grid_dependency_sync();
     const int ks = cluster_size(), part = cluster_cta_rank();
     if (ks != p.ks) {
@@ -113,96 +124,91 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fp8_linear_skinny_kernel(const
         return;
     }
     const int tile = blockIdx.x / ks;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int n0 = tile * kTileN + warp * 16;
     // this CTA's share of the k steps: contiguous, the first `extra` parts take one step more
     const int steps = p.k / kStepBytes;
     const int base = steps / ks, extra = steps % ks;
     const int s_begin = part * base + (part < extra ? part : extra);
-    const int s_end = s_begin + base + (part < extra ? 1 : 0);
+    const int nsteps = base + (part < extra ? 1 : 0);
 
-    const int qn = (p.m + 7) / 8;      // groups of 8 tokens in use
-    float acc[4][4];
+    float acc[QN][4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
+    for (int q = 0; q < QN; ++q)
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[q][e] = 0.f;
 
-    // the two weight rows this thread reads: rows g and g + 8 of the warp's fragment
     // Row-major weights: a k step of the warp's fragment is 64 bytes of 16 rows that lie k bytes apart.  Blocked
     // weights: the same 16 x 64 bytes are one contiguous KiB (row r of the fragment at r * 64) and consecutive k steps
     // follow each other, so a warp streams its fragment's rows as one sequential run of memory.
     const size_t step_stride = p.packed ? 16 * kStepBytes : kStepBytes;
-    const uint8_t *wrow0 = p.packed ? p.w + static_cast<size_t>(n0 / 16) * p.k * 16 + g * kStepBytes + 16 * t
-                                    : p.w + static_cast<size_t>(n0 + g) * p.k + 16 * t;
-    const uint8_t *wrow1 = wrow0 + (p.packed ? static_cast<size_t>(8) * kStepBytes : static_cast<size_t>(8) * p.k);
+    const uint8_t *w0 = (p.packed ? p.w + static_cast<size_t>(n0 / 16) * p.k * 16 + g * kStepBytes + 16 * t
+                                  : p.w + static_cast<size_t>(n0 + g) * p.k + 16 * t) + static_cast<size_t>(s_begin) * step_stride;
+    const size_t half = p.packed ? static_cast<size_t>(8) * kStepBytes : static_cast<size_t>(8) * p.k;
+    const uint8_t *xk = p.x + static_cast<size_t>(s_begin) * kStepBytes;
 
-    // Weights travel through a ring of eight k steps held in registers: a slot is refilled with the step eight ahead
-    // as soon as it has been multiplied, so up to 256 bytes per thread (64 KiB per CTA) are in flight at any time.
-    uint4 ring[kRing][2];
+    auto issue = [&](int j) {      // group j: the weights of step j and, at a chunk start, the activations of the chunk
+        if (j < nsteps) {
+            unsigned char *slot = wring + (j & (kDepth - 1)) * kWSlot + tid * 16;
+            cp_async16(slot, w0, true);
+            cp_async16(slot + kThreads * 16, w0 + half, true);
+            w0 += step_stride;
+            if ((j & (kXSteps - 1)) == 0) {
+                unsigned char *dst = xbuf + ((j / kXSteps) & 1) * kXBuf;
+                const int left = nsteps - j < kXSteps ? nsteps - j : kXSteps;     // steps of this chunk that exist
 #pragma unroll
-    for (int u = 0; u < kRing; ++u)
-        if (s_begin + u < s_end) {
-            ring[u][0] = ld_weights(wrow0 + static_cast<size_t>(s_begin + u) * step_stride);
-            ring[u][1] = ld_weights(wrow1 + static_cast<size_t>(s_begin + u) * step_stride);
-        }
-    for (int s = s_begin; s < s_end; s += kRing) {
-        const int in_chunk = (s - s_begin) % kChunkSteps;
-        if (in_chunk == 0) {
-            // stage the activations of the next 16 k steps (all warps read all of them)
-            const int nsteps = s_end - s < kChunkSteps ? s_end - s : kChunkSteps;
-            __syncthreads();      // everyone is done with the previous round's activations
-            const int row_chunks = nsteps * (kStepBytes / 16);
-            for (int i = threadIdx.x; i < qn * 8 * row_chunks; i += blockDim.x) {
-                const int tok = i / row_chunks, c = i - tok * row_chunks;
-                cp_async16(smem + tok * kXRow + c * 16, p.x + static_cast<size_t>(tok < p.m ? tok : 0) * p.k + static_cast<size_t>(s) * kStepBytes + c * 16,
-                           tok < p.m);
-            }
-            asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
-            __syncthreads();
-        }
-#pragma unroll
-        for (int u = 0; u < kRing; ++u) {
-            const int st = s + u;
-            if (st < s_end) {
-                // the weights are converted once and used for every token group
-                uint32_t w0[8], w1[8];
-                e4m3x16_to_f16(ring[u][0], w0);
-                e4m3x16_to_f16(ring[u][1], w1);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    if (q < qn) {      // token groups that hold no token are skipped (uniform across the CTA)
-                        const uint4 xf = *reinterpret_cast<const uint4 *>(smem + (q * 8 + g) * kXRow + (in_chunk + u) * kStepBytes + 16 * t);
-                        uint32_t xh[8];
-                        e4m3x16_to_f16(xf, xh);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) mma_f16(acc[q], w0[2 * i], w1[2 * i], w0[2 * i + 1], w1[2 * i + 1], xh[2 * i], xh[2 * i + 1]);
-                    }
-                }
-                if (st + kRing < s_end) {
-                    ring[u][0] = ld_weights(wrow0 + static_cast<size_t>(st + kRing) * step_stride);
-                    ring[u][1] = ld_weights(wrow1 + static_cast<size_t>(st + kRing) * step_stride);
+                for (int r = 0; r < QN; ++r) {
+                    const int idx = tid + r * kThreads;
+                    const int tok = idx >> 5, c = idx & 31;      // 32 vectors of 16 bytes per token and chunk
+                    const bool valid = tok < p.m && (c >> 2) < left;
+                    cp_async16(dst + tok * kXRow + c * 16, xk + static_cast<size_t>(valid ? tok : 0) * p.k + static_cast<size_t>(j) * kStepBytes + (valid ? c * 16 : 0),
+                               valid);
                 }
             }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");      // an empty group past the end keeps the count uniform
+    };
+
+#pragma unroll
+    for (int j = 0; j < kDepth - 1; ++j) issue(j);
+    for (int i = 0; i < nsteps; ++i) {
+        issue(i + kDepth - 1);
+        asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");      // group i has landed
+        if ((i & (kXSteps - 1)) == 0) __syncthreads();      // ... for every thread: the chunk's activations are visible
+        const unsigned char *slot = wring + (i & (kDepth - 1)) * kWSlot + tid * 16;
+        // the weights are converted once and used for every token group
+        uint32_t wa[8], wb[8];
+        e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(slot), wa);
+        e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(slot + kThreads * 16), wb);
+        const unsigned char *xs = xbuf + ((i / kXSteps) & 1) * kXBuf + g * kXRow + (i & (kXSteps - 1)) * kStepBytes + 16 * t;
+#pragma unroll
+        for (int q = 0; q < QN; ++q) {
+            uint32_t xh[8];
+            e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(xs + q * 8 * kXRow), xh);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) mma_f16(acc[q], wa[2 * v], wb[2 * v], wa[2 * v + 1], wb[2 * v + 1], xh[2 * v], xh[2 * v + 1]);
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();      // every warp is done with the ring: it becomes the partial tile
 
-    // this CTA's partial tile: channel-major, fp32
-    __syncthreads();
+    // this CTA's partial tile: token-major, fp32 (channels of a token are contiguous, as in the output)
     float *partial = reinterpret_cast<float *>(smem);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < QN; ++q) {
         const int ch = warp * 16 + g, tok = q * 8 + 2 * t;
-        *reinterpret_cast<float2 *>(partial + ch * kPartPitch + tok) = make_float2(acc[q][0], acc[q][1]);
-        *reinterpret_cast<float2 *>(partial + (ch + 8) * kPartPitch + tok) = make_float2(acc[q][2], acc[q][3]);
+        partial[tok * kPartPitch + ch] = acc[q][0];
+        partial[(tok + 1) * kPartPitch + ch] = acc[q][1];
+        partial[tok * kPartPitch + ch + 8] = acc[q][2];
+        partial[(tok + 1) * kPartPitch + ch + 8] = acc[q][3];
     }
     cluster_barrier();
     // CTA `part` finishes channels [part * per, part * per + per) of the tile: sum over the cluster in CTA order
     const int per = kTileN / ks;
-    for (int e = threadIdx.x; e < per * kTokens; e += blockDim.x) {
+    for (int e = tid; e < per * QN * 8; e += kThreads) {
         const int ch = part * per + e % per, tok = e / per;
         float sum = 0.f;
-        for (int c = 0; c < ks; ++c) sum += ld_cluster_f32(partial + ch * kPartPitch + tok, c);
+        for (int c = 0; c < ks; ++c) sum += ld_cluster_f32(partial + tok * kPartPitch + ch, c);
         const int n = tile * kTileN + ch;
         if (tok < p.m) p.out[static_cast<size_t>(tok) * p.n + n] = __float2bfloat16_rn(sum * p.x_scale[tok] * p.w_scale[n]);
     }
@@ -262,9 +268,17 @@ extern "C" int gpuk_fp8_linear_skinny(const void *x_fp8, const float *x_scale, c
     }
     Fp8LinearParams p = {static_cast<const uint8_t *>(x_fp8), x_scale, static_cast<const uint8_t *>(w_fp8), w_scale,
                          static_cast<__nv_bfloat16 *>(out_bf16), m, n, k, ks, w_layout, status_by_device[device]};
+    const void *fns[4] = {reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<1>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<2>),
+                          reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<3>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<4>)};
+    const int qn = (m + 7) / 8;
+    static bool smem_opted_in[64][4] = {};      // per device and instantiation: more than 48 KiB of dynamic shared memory
+    if (!smem_opted_in[device][qn - 1]) {
+        cudaError_t ea = cudaFuncSetAttribute(fns[qn - 1], cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (ea != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "fp8_linear: cannot opt in to %d bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(ea));
+        smem_opted_in[device][qn - 1] = true;
+    }
     void *args[] = {&p};
-    cudaError_t e = launch_kernel(reinterpret_cast<const void *>(&fp8_linear_skinny_kernel), (n / kTileN) * ks, kWarps * 32, ks, false, args,
-                                  static_cast<cudaStream_t>(stream));
+    cudaError_t e = launch_kernel(fns[qn - 1], (n / kTileN) * ks, kThreads, ks, false, args, static_cast<cudaStream_t>(stream), kSmemBytes);
     if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "fp8_linear: launch failed: %s", cudaGetErrorString(e));
     return GPUK_OK;
 }

@@ -12,10 +12,10 @@ replaces ``reduce_from_tensor_parallel_region`` + ``x + ...`` + the following ``
 (``tensor_parallel.py:117-118``, ``transformer_model.py:610-618``) at both sites of every
 layer.  With ``fp8=True`` the normalised activations leave the operator as FP8-e4m3 with one
 scale per token, and the column-parallel projections that consume them run as FP8 GEMMs with
-row-wise scales: ``torch._scaled_mm`` (a library GEMM) by default, or -- ``own_fp8_gemm=True``, decode batches of
-at most 32 tokens -- this library's own weight-streaming kernel (``gpuk_b200.fp8_linear``, ``csrc/fp8_linear.cu``),
-which gives the same results to within one bf16 step and is slower than the library on B200 at the
-benchmark's shapes (measured in ``bench.py --case fp8_linear``).
+row-wise scales: for decode batches this library's own weight-streaming kernel (``gpuk_b200.fp8_linear``,
+``csrc/fp8_linear.cu``) where it is the faster one on B200 (up to 16 tokens, or up to 32 tokens and at most 4096
+output channels per shard; measured in ``bench.py --case fp8_linear``), otherwise ``torch._scaled_mm`` (a library
+GEMM; ``own_fp8_gemm=False`` uses it everywhere).  Both give the same results to within one bf16 step.
 
 ``fused=False`` runs the reference arrangement on the same weights -- NCCL ``all_reduce``, then
 add, RMSNorm (and quantisation) as separate PyTorch operators -- and is the comparison arm.
@@ -72,7 +72,7 @@ def _xavier(out_f: int, in_f: int, gen: torch.Generator, device, dtype) -> torch
 class _Linear:
     """y = x @ W^T for one shard, in the activation dtype or as an FP8 GEMM with row-wise scales."""
 
-    def __init__(self, weight: torch.Tensor, fp8: bool, own_gemm: bool = False):
+    def __init__(self, weight: torch.Tensor, fp8: bool, own_gemm: bool = True):
         self.weight = weight                                  # [out_local, in]
         self.fp8 = fp8
         self.own_gemm = own_gemm                              # decode batches: this library's weight-streaming FP8 kernel
@@ -86,7 +86,11 @@ class _Linear:
         if self.fp8 and x.dtype == torch.float8_e4m3fn:
             if self.own_gemm and x.is_cuda:
                 import gpuk_b200 as gpuk
-                if gpuk.fp8_linear_supported(x.shape[0], self.w_q.shape[0], self.w_q.shape[1]) and self.weight.dtype == torch.bfloat16:
+                # measured on B200 (bench.py --case fp8_linear): faster than the library GEMM up to 16 tokens at every
+                # shape of the decoder, and up to 32 tokens where the shard has at most 4096 output channels
+                m, n = x.shape[0], self.w_q.shape[0]
+                if (gpuk.fp8_linear_supported(m, n, self.w_q.shape[1]) and (m <= 16 or n <= 4096)
+                        and self.weight.dtype == torch.bfloat16):
                     if self.w_packed is None:
                         self.w_packed = gpuk.fp8_pack_weight(self.w_q)
                     return gpuk.fp8_linear(x, x_scale, self.w_packed, self.w_scale, packed=True)
@@ -98,7 +102,7 @@ class TPDecoder:
     """Random-initialised decoder, sharded over the ranks of ``env``'s group; inference only."""
 
     def __init__(self, args: DecoderArgs, env, *, device, fused: bool = True, fp8: bool = True, seed: int = 1234,
-                 master_init: bool = False, max_batch: int = 32, own_fp8_gemm: bool = False):
+                 master_init: bool = False, max_batch: int = 32, own_fp8_gemm: bool = True):
         self.args, self.env, self.device, self.fused, self.fp8 = args, env, torch.device(device), fused, fp8
         self.rank, self.world = env.rank, env.world_size
         a, w, r = args, self.world, self.rank
