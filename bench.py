@@ -397,7 +397,8 @@ def run_model(env, rank, world, steps, warmup, barrier):
     tokens = torch.randint(0, args.vocab_size, (batch, 1), generator=torch.Generator().manual_seed(11)).to(device)
     pos = torch.tensor([ctx], device=device)
     for name, fused in (("fused", True), ("nccl_unfused", False)):
-        model = TPDecoder(args, env, device=device, fused=fused, fp8=True, max_batch=batch)
+        # the comparison arm is the reference arrangement throughout: NCCL, unfused operators, library GEMMs
+        model = TPDecoder(args, env, device=device, fused=fused, fp8=True, max_batch=batch, own_fp8_gemm=fused)
         model.fill_kv_cache(ctx)
 
         def step(_):
@@ -1142,6 +1143,12 @@ def main():
                 sweep.append(run_model(env, rank, world, max(10, min(args.steps, 100)), 5, barrier))
             except Exception as e:
                 sweep.append({"workload": "c5_decoder", "error": repr(e)[:300]})
+            if world == 1:
+                # the linear layer behind the operator, per rank of the eight-way decoder: own kernel beside the library GEMM
+                try:
+                    sweep.append({"workload": "c5_fp8_linear_32_tokens_per_rank_of_8", **run_fp8_linear(32, 100)})
+                except Exception as e:
+                    sweep.append({"workload": "c5_fp8_linear_32_tokens_per_rank_of_8", "error": repr(e)[:300]})
 
     crossover = run_crossover(env, gpuk, rank, world, barrier) if (args.crossover and world > 1) else None
     overlap = None
