@@ -32,6 +32,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <mutex>
 
 #include "../../include/gpuk_b200.h"
 #include "launch.cuh"
@@ -258,25 +259,29 @@ extern "C" int gpuk_fp8_linear_skinny(const void *x_fp8, const float *x_scale, c
         ks = 1;
         while (ks < 8 && (n / kTileN) * ks * 2 <= 2 * sms && k / kStepBytes >= 8 * ks) ks *= 2;
     }
-    int **status_by_device = g_status_by_device;
     if (device < 0 || device >= 64) return set_last_error(GPUK_ERR_UNSUPPORTED, "fp8_linear: device index %d", device);
-    if (!status_by_device[device]) {
-        int *s = nullptr;
-        if (cudaMalloc(&s, sizeof(int)) != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "fp8_linear: cannot allocate the status word");
-        clear_status_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(s);
-        status_by_device[device] = s;
-    }
-    Fp8LinearParams p = {static_cast<const uint8_t *>(x_fp8), x_scale, static_cast<const uint8_t *>(w_fp8), w_scale,
-                         static_cast<__nv_bfloat16 *>(out_bf16), m, n, k, ks, w_layout, status_by_device[device]};
     const void *fns[4] = {reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<1>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<2>),
                           reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<3>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<4>)};
-    const int qn = (m + 7) / 8;
-    static bool smem_opted_in[64][4] = {};      // per device and instantiation: more than 48 KiB of dynamic shared memory
-    if (!smem_opted_in[device][qn - 1]) {
-        cudaError_t ea = cudaFuncSetAttribute(fns[qn - 1], cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (ea != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "fp8_linear: cannot opt in to %d bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(ea));
-        smem_opted_in[device][qn - 1] = true;
+    {
+        // first call on a device (guarded for concurrent callers): the status word, and the opt-in to more than
+        // 48 KiB of dynamic shared memory for every instantiation, so that no later call has set-up left to do
+        static std::mutex init_mutex;
+        std::lock_guard<std::mutex> lock(init_mutex);
+        if (!g_status_by_device[device]) {
+            for (const void *fn : fns) {
+                cudaError_t ea = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+                if (ea != cudaSuccess)
+                    return set_last_error(GPUK_ERR_CUDA, "fp8_linear: cannot opt in to %d bytes of shared memory: %s", kSmemBytes, cudaGetErrorString(ea));
+            }
+            int *s = nullptr;
+            if (cudaMalloc(&s, sizeof(int)) != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "fp8_linear: cannot allocate the status word");
+            clear_status_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(s);
+            g_status_by_device[device] = s;
+        }
     }
+    Fp8LinearParams p = {static_cast<const uint8_t *>(x_fp8), x_scale, static_cast<const uint8_t *>(w_fp8), w_scale,
+                         static_cast<__nv_bfloat16 *>(out_bf16), m, n, k, ks, w_layout, g_status_by_device[device]};
+    const int qn = (m + 7) / 8;
     void *args[] = {&p};
     cudaError_t e = launch_kernel(fns[qn - 1], (n / kTileN) * ks, kThreads, ks, false, args, static_cast<cudaStream_t>(stream), kSmemBytes);
     if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "fp8_linear: launch failed: %s", cudaGetErrorString(e));
