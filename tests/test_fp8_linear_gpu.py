@@ -106,3 +106,19 @@ def test_shapes_outside_the_kernels_range_are_refused_before_any_cuda_call():
     assert f(null, null, null, null, null, 0, 128, 64, 0, 0, None) == cabi.OK          # no tokens: nothing to do
     assert cabi.lib.gpuk_fp8_pack_weight(null, ctypes.c_void_p(32), 24, 64, None) == cabi.ERR_UNSUPPORTED
     assert cabi.lib.gpuk_fp8_pack_weight(null, null, 16, 64, None) == cabi.ERR_INVALID_ARGUMENT      # in place
+
+
+def test_python_wrapper_refuses_what_the_kernel_cannot_take():
+    """gpuk_b200.fp8_linear on the host side: shapes it is built for, and operands it must refuse before any launch."""
+    import gpuk_b200 as gpuk
+    assert gpuk.fp8_linear_supported(32, 7168, 8192) and gpuk.fp8_linear_supported(1, 128, 64)
+    assert not gpuk.fp8_linear_supported(33, 7168, 8192) and not gpuk.fp8_linear_supported(0, 128, 64)
+    assert not gpuk.fp8_linear_supported(8, 100, 64) and not gpuk.fp8_linear_supported(8, 128, 96)
+    x = torch.zeros(8, 64).to(E4M3)
+    w = torch.zeros(128, 64).to(E4M3)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        gpuk.fp8_linear(x, torch.ones(8, 1), w, torch.ones(1, 128))            # host tensors
+    with pytest.raises(RuntimeError, match="float8_e4m3fn"):
+        gpuk.fp8_linear(x.float(), torch.ones(8, 1), w, torch.ones(1, 128))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        gpuk.fp8_pack_weight(w)
