@@ -1011,8 +1011,10 @@ def run_case(a):
         print("norm_quant", a.tokens, a.hidden, "scale0", float(scale[0]))
         return
     if a.case == "fp8_linear":
-        for tokens in ([a.tokens] if a.tokens <= 32 else [8, 16, 32]):
-            print(json.dumps(run_fp8_linear(tokens, a.iters)), flush=True)
+        for frags in ([1, 2] if a.frags < 0 else [a.frags]):      # --frags -1: both settings, one after the other
+            cabi.check(cabi.lib.gpuk_set_tuning(b"fp8_frags_per_warp", frags))
+            for tokens in ([a.tokens] if a.tokens <= 32 else [8, 16, 32]):
+                print(json.dumps({"fp8_frags_per_warp": frags, **run_fp8_linear(tokens, a.iters)}), flush=True)
         return
     n = a.world
     msg = a.tokens * a.hidden * 2
@@ -1070,6 +1072,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=8192)
     ap.add_argument("--quant", type=int, default=3)
+    ap.add_argument("--frags", type=int, default=0, help="--case fp8_linear: fragments per warp (0: default, -1: time 1 and 2)")
     ap.add_argument("--iters", type=int, default=6)
     ap.add_argument("--world", type=int, default=8)
     ap.add_argument("--mode", type=int, default=2)

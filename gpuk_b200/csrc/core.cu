@@ -1019,6 +1019,9 @@ int gpuk_set_tuning(const char *name, int64_t value) {
         g_tuning.k1_threads = static_cast<int>(value);
     } else if (n == "k1_staged_min_rows") {
         g_tuning.k1_staged_min_rows = value;
+    } else if (n == "fp8_frags_per_warp") {
+        if (value < 0 || value > 2) return fail(GPUK_ERR_INVALID_ARGUMENT, "fp8_frags_per_warp must be 0, 1 or 2");
+        fp8_frags_per_warp_tuning = static_cast<int>(value);
     } else if (n == "k1_ctas_per_sm") {
         if (value < 0 || value > 8) return fail(GPUK_ERR_INVALID_ARGUMENT, "k1_ctas_per_sm must be in [0, 8]");
         g_tuning.k1_ctas_per_sm = static_cast<int>(value);

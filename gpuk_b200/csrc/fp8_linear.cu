@@ -113,10 +113,14 @@ __device__ __forceinline__ float ld_cluster_f32(const float *local, int cta) {
 // steps, all threads together fetch that chunk (every token's 512 bytes) into the activation buffer the chunk
 // before last used, inside the same group; when the multiply front enters the chunk, every thread has waited for
 // its own copies and one block barrier makes the chunk visible to all warps.
-template <int QN>
-__global__ void __launch_bounds__(kThreads, 2) fp8_linear_skinny_kernel(const __grid_constant__ Fp8LinearParams p) {
+//
+// FR = 16-row fragments per warp (1: eight warps per CTA, 2: four).  With two fragments a warp converts an
+// activation vector once for both, and the per-step bookkeeping is shared: worth it when there are many token groups.
+template <int QN, int FR>
+__global__ void __launch_bounds__(kThreads / FR, 2) fp8_linear_skinny_kernel(const __grid_constant__ Fp8LinearParams p) {
+    constexpr int T = kThreads / FR;                      // threads per CTA; FR * T 16-byte vectors per half fragment row set
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char *wring = smem;                          // [kDepth][2][kThreads] x 16 bytes
+    unsigned char *wring = smem;                          // [kDepth][2 * FR][T] x 16 bytes
     unsigned char *xbuf = smem + kDepth * kWSlot;         // [2][kTokens][kXRow]
     grid_dependency_sync();
     const int ks = cluster_size(), part = cluster_cta_rank();
@@ -126,18 +130,20 @@ __global__ void __launch_bounds__(kThreads, 2) fp8_linear_skinny_kernel(const __
     }
     const int tile = blockIdx.x / ks;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int n0 = tile * kTileN + warp * 16;
+    const int n0 = tile * kTileN + warp * FR * 16;      // the warp's first fragment; the next one 16 channels on
     // this CTA's share of the k steps: contiguous, the first `extra` parts take one step more
     const int steps = p.k / kStepBytes;
     const int base = steps / ks, extra = steps % ks;
     const int s_begin = part * base + (part < extra ? part : extra);
     const int nsteps = base + (part < extra ? 1 : 0);
 
-    float acc[QN][4];
+    float acc[FR][QN][4];
 #pragma unroll
-    for (int q = 0; q < QN; ++q)
+    for (int f = 0; f < FR; ++f)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[q][e] = 0.f;
+        for (int q = 0; q < QN; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[f][q][e] = 0.f;
 
     // Row-major weights: a k step of the warp's fragment is 64 bytes of 16 rows that lie k bytes apart.  Blocked
     // weights: the same 16 x 64 bytes are one contiguous KiB (row r of the fragment at r * 64) and consecutive k steps
@@ -146,20 +152,24 @@ __global__ void __launch_bounds__(kThreads, 2) fp8_linear_skinny_kernel(const __
     const uint8_t *w0 = (p.packed ? p.w + static_cast<size_t>(n0 / 16) * p.k * 16 + g * kStepBytes + 16 * t
                                   : p.w + static_cast<size_t>(n0 + g) * p.k + 16 * t) + static_cast<size_t>(s_begin) * step_stride;
     const size_t half = p.packed ? static_cast<size_t>(8) * kStepBytes : static_cast<size_t>(8) * p.k;
+    const size_t frag = static_cast<size_t>(16) * p.k;      // from one fragment to the next: 16 rows, in either layout
     const uint8_t *xk = p.x + static_cast<size_t>(s_begin) * kStepBytes;
 
     auto issue = [&](int j) {      // group j: the weights of step j and, at a chunk start, the activations of the chunk
         if (j < nsteps) {
             unsigned char *slot = wring + (j & (kDepth - 1)) * kWSlot + tid * 16;
-            cp_async16(slot, w0, true);
-            cp_async16(slot + kThreads * 16, w0 + half, true);
+#pragma unroll
+            for (int f = 0; f < FR; ++f) {
+                cp_async16(slot + (2 * f) * T * 16, w0 + f * frag, true);
+                cp_async16(slot + (2 * f + 1) * T * 16, w0 + f * frag + half, true);
+            }
             w0 += step_stride;
             if ((j & (kXSteps - 1)) == 0) {
                 unsigned char *dst = xbuf + ((j / kXSteps) & 1) * kXBuf;
                 const int left = nsteps - j < kXSteps ? nsteps - j : kXSteps;     // steps of this chunk that exist
 #pragma unroll
-                for (int r = 0; r < QN; ++r) {
-                    const int idx = tid + r * kThreads;
+                for (int r = 0; r < QN * FR; ++r) {
+                    const int idx = tid + r * T;
                     const int tok = idx >> 5, c = idx & 31;      // 32 vectors of 16 bytes per token and chunk
                     const bool valid = tok < p.m && (c >> 2) < left;
                     cp_async16(dst + tok * kXRow + c * 16, xk + static_cast<size_t>(valid ? tok : 0) * p.k + static_cast<size_t>(j) * kStepBytes + (valid ? c * 16 : 0),
@@ -177,17 +187,23 @@ __global__ void __launch_bounds__(kThreads, 2) fp8_linear_skinny_kernel(const __
         asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");      // group i has landed
         if ((i & (kXSteps - 1)) == 0) __syncthreads();      // ... for every thread: the chunk's activations are visible
         const unsigned char *slot = wring + (i & (kDepth - 1)) * kWSlot + tid * 16;
-        // the weights are converted once and used for every token group
-        uint32_t wa[8], wb[8];
-        e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(slot), wa);
-        e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(slot + kThreads * 16), wb);
+        // the weights are converted once and used for every token group, an activation vector once for every fragment
+        uint32_t wa[FR][8], wb[FR][8];
+#pragma unroll
+        for (int f = 0; f < FR; ++f) {
+            e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(slot + (2 * f) * T * 16), wa[f]);
+            e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(slot + (2 * f + 1) * T * 16), wb[f]);
+        }
         const unsigned char *xs = xbuf + ((i / kXSteps) & 1) * kXBuf + g * kXRow + (i & (kXSteps - 1)) * kStepBytes + 16 * t;
 #pragma unroll
         for (int q = 0; q < QN; ++q) {
             uint32_t xh[8];
             e4m3x16_to_f16(*reinterpret_cast<const uint4 *>(xs + q * 8 * kXRow), xh);
 #pragma unroll
-            for (int v = 0; v < 4; ++v) mma_f16(acc[q], wa[2 * v], wb[2 * v], wa[2 * v + 1], wb[2 * v + 1], xh[2 * v], xh[2 * v + 1]);
+            for (int v = 0; v < 4; ++v)
+#pragma unroll
+                for (int f = 0; f < FR; ++f)
+                    mma_f16(acc[f][q], wa[f][2 * v], wb[f][2 * v], wa[f][2 * v + 1], wb[f][2 * v + 1], xh[2 * v], xh[2 * v + 1]);
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -196,17 +212,19 @@ __global__ void __launch_bounds__(kThreads, 2) fp8_linear_skinny_kernel(const __
     // this CTA's partial tile: token-major, fp32 (channels of a token are contiguous, as in the output)
     float *partial = reinterpret_cast<float *>(smem);
 #pragma unroll
-    for (int q = 0; q < QN; ++q) {
-        const int ch = warp * 16 + g, tok = q * 8 + 2 * t;
-        partial[tok * kPartPitch + ch] = acc[q][0];
-        partial[(tok + 1) * kPartPitch + ch] = acc[q][1];
-        partial[tok * kPartPitch + ch + 8] = acc[q][2];
-        partial[(tok + 1) * kPartPitch + ch + 8] = acc[q][3];
-    }
+    for (int f = 0; f < FR; ++f)
+#pragma unroll
+        for (int q = 0; q < QN; ++q) {
+            const int ch = (warp * FR + f) * 16 + g, tok = q * 8 + 2 * t;
+            partial[tok * kPartPitch + ch] = acc[f][q][0];
+            partial[(tok + 1) * kPartPitch + ch] = acc[f][q][1];
+            partial[tok * kPartPitch + ch + 8] = acc[f][q][2];
+            partial[(tok + 1) * kPartPitch + ch + 8] = acc[f][q][3];
+        }
     cluster_barrier();
     // CTA `part` finishes channels [part * per, part * per + per) of the tile: sum over the cluster in CTA order
     const int per = kTileN / ks;
-    for (int e = tid; e < per * QN * 8; e += kThreads) {
+    for (int e = tid; e < per * QN * 8; e += T) {
         const int ch = part * per + e % per, tok = e / per;
         float sum = 0.f;
         for (int c = 0; c < ks; ++c) sum += ld_cluster_f32(partial + tok * kPartPitch + ch, c);
@@ -235,6 +253,8 @@ int *g_status_by_device[64] = {};   // one device word per GPU, allocated by the
 }  // namespace
 }  // namespace gpuk
 
+int gpuk::fp8_frags_per_warp_tuning = 0;
+
 using namespace gpuk;
 
 extern "C" int gpuk_fp8_linear_skinny(const void *x_fp8, const float *x_scale, const void *w_fp8, const float *w_scale,
@@ -260,8 +280,12 @@ extern "C" int gpuk_fp8_linear_skinny(const void *x_fp8, const float *x_scale, c
         while (ks < 8 && (n / kTileN) * ks * 2 <= 2 * sms && k / kStepBytes >= 8 * ks) ks *= 2;
     }
     if (device < 0 || device >= 64) return set_last_error(GPUK_ERR_UNSUPPORTED, "fp8_linear: device index %d", device);
-    const void *fns[4] = {reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<1>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<2>),
-                          reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<3>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<4>)};
+    // one fragment per warp (eight warps), or two (four warps) for more than 16 tokens on 4096 channels or more: measured
+    // at 32 tokens, one / two fragments: n = 1280 9.1 / 10.3 us, n = 4096 14.0 / 13.1 us, n = 7168 21.8 / 21.2 us (k = 8192)
+    const void *fns[8] = {reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<1, 1>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<2, 1>),
+                          reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<3, 1>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<4, 1>),
+                          reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<1, 2>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<2, 2>),
+                          reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<3, 2>), reinterpret_cast<const void *>(&fp8_linear_skinny_kernel<4, 2>)};
     {
         // first call on a device (guarded for concurrent callers): the status word, and the opt-in to more than
         // 48 KiB of dynamic shared memory for every instantiation, so that no later call has set-up left to do
@@ -282,8 +306,9 @@ extern "C" int gpuk_fp8_linear_skinny(const void *x_fp8, const float *x_scale, c
     Fp8LinearParams p = {static_cast<const uint8_t *>(x_fp8), x_scale, static_cast<const uint8_t *>(w_fp8), w_scale,
                          static_cast<__nv_bfloat16 *>(out_bf16), m, n, k, ks, w_layout, g_status_by_device[device]};
     const int qn = (m + 7) / 8;
+    const int fr = (fp8_frags_per_warp_tuning == 1 || fp8_frags_per_warp_tuning == 2) ? fp8_frags_per_warp_tuning : ((qn >= 3 && n >= 4096) ? 2 : 1);
     void *args[] = {&p};
-    cudaError_t e = launch_kernel(fns[qn - 1], (n / kTileN) * ks, kThreads, ks, false, args, static_cast<cudaStream_t>(stream), kSmemBytes);
+    cudaError_t e = launch_kernel(fns[(fr - 1) * 4 + qn - 1], (n / kTileN) * ks, kThreads / fr, ks, false, args, static_cast<cudaStream_t>(stream), kSmemBytes);
     if (e != cudaSuccess) return set_last_error(GPUK_ERR_CUDA, "fp8_linear: launch failed: %s", cudaGetErrorString(e));
     return GPUK_OK;
 }

@@ -53,6 +53,10 @@ cudaError_t launch_ar_emulated(const ArParams *params_by_rank, const ArShape &s,
 template <typename T>
 cudaError_t ar_resident_ctas(const ArShape &s, bool emulated, int sm_count, int64_t *ctas);
 
+// Process-wide tuning of the FP8 linear layer (gpuk_set_tuning "fp8_frags_per_warp"): 16-row fragments per warp,
+// 1 or 2; 0 = chosen from the shape.  Defined in fp8_linear.cu.
+extern int fp8_frags_per_warp_tuning;
+
 // Quantisation policy of an operator quant_type (include/gpuk_b200.h); false for an unknown one.
 bool quant_from_type(int quant_type, Quant *q);
 

@@ -279,7 +279,10 @@ int gpuk_ws_set_option(gpuk_ws *ws, const char *name, int64_t value);
  * workspace to carry options): "k1_stages" (shared-memory stages of the persistent variant: 2, 3,
  * 0 = never use it, -1 = default), "k1_staged_min_rows" (rows from which that variant runs,
  * -1 = default: more rows than the plain kernel has resident CTAs), "k1_ctas_per_sm" (cap on its
- * resident CTAs per SM, 0 = as many as fit).  Not thread-safe against concurrent calls.
+ * resident CTAs per SM, 0 = as many as fit).  One more name belongs to gpuk_fp8_linear_skinny:
+ * "fp8_frags_per_warp" (16-row fragments a warp multiplies per k step: 1 = eight warps per CTA, 2 = four warps
+ * that convert each activation vector once for two fragments; 0 = default: 2 for more than 16 tokens on at least 4096 output channels, else 1).
+ * Not thread-safe against concurrent calls.
  */
 int gpuk_set_tuning(const char *name, int64_t value);
 /* Budget of every device-side wait for a peer, in nanoseconds (default 2 s). */

@@ -23,7 +23,15 @@ def _want(x, xs, w, ws):
     return (x.double() @ w.double().t()) * xs.double() * ws.double()
 
 
-def _run(x, xs, w, ws, k_split=0, packed=False):
+def _run(x, xs, w, ws, k_split=0, packed=False, frags=0):
+    cabi.check(cabi.lib.gpuk_set_tuning(b"fp8_frags_per_warp", frags))
+    try:
+        return _run_with_current_tuning(x, xs, w, ws, k_split, packed)
+    finally:
+        cabi.check(cabi.lib.gpuk_set_tuning(b"fp8_frags_per_warp", 0))
+
+
+def _run_with_current_tuning(x, xs, w, ws, k_split, packed):
     m, k = x.shape
     n = w.shape[0]
     dx, dxs, dw, dws = x.cuda(), xs.cuda().contiguous(), w.cuda(), ws.cuda().contiguous()
@@ -54,15 +62,16 @@ def _close(got, want):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("frags", [1, 2])
 @pytest.mark.parametrize("packed", [False, True])
 @pytest.mark.parametrize("k_split", [0, 1, 2, 4, 8])
 @pytest.mark.parametrize("m,n,k", [(32, 128, 64), (1, 256, 8192), (8, 1280, 8192), (17, 7168, 1024), (32, 1024, 3584), (31, 384, 4160)])
-def test_matches_float64_product(m, n, k, k_split, packed):
+def test_matches_float64_product(m, n, k, k_split, packed, frags):
     """Token counts that leave groups of 8 partly or wholly empty, k that does not divide over the cluster
     (3584 / 64 = 56 steps over 8 parts, 4160 / 64 = 65), one k step only, every cluster size, both weight layouts
-    (the blocked one is also compared with the same rearrangement done by PyTorch)."""
+    (the blocked one is also compared with the same rearrangement done by PyTorch), one and two fragments per warp."""
     x, xs, w, ws = _case(m, n, k, seed=m * 7 + n + k)
-    _close(_run(x, xs, w, ws, k_split, packed), _want(x, xs, w, ws))
+    _close(_run(x, xs, w, ws, k_split, packed, frags), _want(x, xs, w, ws))
 
 
 @pytest.mark.gpu
@@ -73,6 +82,7 @@ def test_reproducible_and_close_to_the_library_gemm():
     b = _run(x, xs, w, ws)
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))      # fixed summation order
     assert torch.equal(a.view(torch.int16), _run(x, xs, w, ws, packed=True).view(torch.int16))      # ... whatever the weight layout
+    assert torch.equal(a.view(torch.int16), _run(x, xs, w, ws, frags=1).view(torch.int16))          # ... and the warps' share
     lib = torch._scaled_mm(x.cuda(), w.cuda().t(), scale_a=xs.cuda(), scale_b=ws.cuda(), out_dtype=torch.bfloat16).cpu()
     _close(lib, _want(x, xs, w, ws))
     # both are within a bf16 step of the float64 product (the library accumulates less exactly): mostly the same bits
