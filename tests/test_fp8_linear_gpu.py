@@ -6,6 +6,7 @@ import pytest
 import torch
 
 from gpuk_b200 import cabi
+from oracle import fp8_linear_oracle as fo
 
 E4M3 = torch.float8_e4m3fn
 
@@ -20,7 +21,7 @@ def _case(m, n, k, seed):
 
 
 def _want(x, xs, w, ws):
-    return (x.double() @ w.double().t()) * xs.double() * ws.double()
+    return fo.fp8_linear_reference(x, xs, w, ws)
 
 
 def _run(x, xs, w, ws, k_split=0, packed=False, frags=0):
@@ -55,10 +56,17 @@ def _run_with_current_tuning(x, xs, w, ws, k_split, packed):
 def _close(got, want):
     """fp32 accumulation of exact FP8 products, one rounding to bf16: within one bf16 step (2^-8 relative) of the
     float64 result, plus the accumulation error of k terms (far below that)."""
-    assert torch.isfinite(got.float()).all()
-    err = (got.double() - want).abs()
-    tol = want.abs() * 2.0 ** -7 + want.abs().max() * 1e-6
-    assert bool((err <= tol).all()), (float(err.max()), float(want.abs().max()))
+    assert fo.within_one_bf16_step(got, want), (float((got.double() - want).abs().max()), float(want.abs().max()))
+
+
+def test_oracle_on_known_answers():
+    """The float64 restatement on values small enough to check by hand, and its tolerance helper."""
+    x = torch.tensor([[1.0, 2.0, -0.5, 0.0] * 16]).to(E4M3)              # one token, k = 64
+    w = torch.tensor([[2.0, 1.0, 4.0, 448.0] * 16, [0.5] * 64]).to(E4M3)
+    y = fo.fp8_linear_reference(x, torch.tensor([[0.5]]), w, torch.tensor([[2.0, 4.0]]))
+    assert y.tolist() == [[16 * (2.0 + 2.0 - 2.0) * 0.5 * 2.0, 16 * (0.5 + 1.0 - 0.25) * 0.5 * 4.0]]
+    assert fo.within_one_bf16_step(y.to(torch.bfloat16), y)
+    assert not fo.within_one_bf16_step((y * 1.02).to(torch.bfloat16), y)
 
 
 @pytest.mark.gpu
