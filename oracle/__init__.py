@@ -9,4 +9,8 @@ Pinned against: golden vectors produced by running the reference's own Python
 (``gpuk/__init__.py:147-173``) over gloo, stored in ``tests/golden``; and against the
 reference's software FP8 conversion (``src/common/float8.h:17-150``) compiled from its
 sources into ``oracle/_ref``.
+
+``fp8_linear_oracle`` states, in float64, what the linear layer that consumes the operator's FP8
+output must compute (the reference has no FP8 linear layer; the definition follows from the
+operator's own quantisation rule) and is pinned by a known-answer test.
 """
