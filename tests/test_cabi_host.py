@@ -112,3 +112,13 @@ def test_plan_tiles_respect_the_kernels_launch_bounds(world):
 
 def test_attach_symmetric_validates_before_touching_cuda():
     assert cabi.lib.gpuk_ws_attach_symmetric(None, None, 2, None, 1 << 20) == cabi.ERR_INVALID_ARGUMENT
+
+
+def test_tuning_names_and_ranges():
+    """gpuk_set_tuning: process-wide knobs of the entry points that have no workspace; pure host state."""
+    assert cabi.lib.gpuk_set_tuning(b"fp8_frags_per_warp", 2) == cabi.OK
+    assert cabi.lib.gpuk_set_tuning(b"fp8_frags_per_warp", 3) == cabi.ERR_INVALID_ARGUMENT
+    assert cabi.lib.gpuk_set_tuning(b"fp8_frags_per_warp", 0) == cabi.OK
+    assert cabi.lib.gpuk_set_tuning(b"k1_stages", 9) == cabi.ERR_INVALID_ARGUMENT
+    assert cabi.lib.gpuk_set_tuning(b"no_such_knob", 1) == cabi.ERR_INVALID_ARGUMENT and "no_such_knob" in cabi.last_error()
+    assert cabi.lib.gpuk_set_tuning(None, 1) == cabi.ERR_INVALID_ARGUMENT
